@@ -4,8 +4,10 @@ from .llama import Llama3RopeScaling, LlamaConfig
 from .torirax import DeltaMixerConfig, DiffAttentionConfig, ToriraxConfig, ToriraxLayerConfig
 from .vegodra import (ChunkedAttentionConfig, GlaConfig, LatentAttentionConfig, RotaryConfig, VegodraConfig,
                       VegodraLayerConfig)
+from .runopel import DenseFFConfig, Mamba2Config, RoutedFFConfig, RunopelConfig, RunopelLayerConfig, WindowLatentConfig
 
 __all__ = ["Architecture", "ConfigError", "ModelConfig", "config_from_dict", "get_architecture", "load_config",
            "register_architecture", "registered_architectures", "save_config", "take", "Llama3RopeScaling",
            "LlamaConfig", "DeltaMixerConfig", "DiffAttentionConfig", "ToriraxConfig", "ToriraxLayerConfig",
-           "ChunkedAttentionConfig", "GlaConfig", "LatentAttentionConfig", "RotaryConfig", "VegodraConfig", "VegodraLayerConfig"]
+           "ChunkedAttentionConfig", "GlaConfig", "LatentAttentionConfig", "RotaryConfig", "VegodraConfig", "VegodraLayerConfig",
+           "DenseFFConfig", "Mamba2Config", "RoutedFFConfig", "RunopelConfig", "RunopelLayerConfig", "WindowLatentConfig"]

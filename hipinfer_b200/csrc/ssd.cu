@@ -1,0 +1,311 @@
+// The state-space mixer with a scalar decay per head (state-space duality), in three kernels.
+//
+// From one 32-bit projection result per token, [z (H P) | x (H P) | B (G N) | C (G N) | dt (H)]:
+//   ssd_conv_kernel       (x, B, C) <- silu(causal convolution over the token axis, K taps a channel, + bias); the last K - 1
+//                         raw inputs of a request are carried in its state slot, zeros before the sequence
+//   ssd_scan_kernel       per head h (group g = h / (H / G)), with a state S [N][P] carried in 32-bit from token to token:
+//                             dt = softplus(dt_raw + dt_bias_h);  a = exp(-exp(A_log_h) dt)
+//                             S <- a S + (dt B_g) x_h^T;  y = S^T C_g + D_h x_h
+//   ssd_gate_norm_kernel  y <- y silu(z), then the row in `parts` equal parts, each divided by its own root mean square
+//                         (eps inside the root) and multiplied by a weight; rounded once
+// Everything here is 32-bit. Requests, lengths and state slots come from device arrays, so a decode step can be replayed
+// from a CUDA graph; a token's arithmetic does not depend on where a portion or a chunk starts.
+#include "common.cuh"
+
+constexpr int SC_TAPS_MAX = 8;     // most convolution taps
+constexpr int SC_CHUNK = 64;       // tokens a block of the convolution walks
+constexpr int SC_THREADS = 128;
+
+// grid (channel tiles, requests, token chunks); a thread owns a channel and walks its chunk's tokens with the K - 1 raw
+// inputs before them in registers. Only the block of a request's first chunk reads the carried inputs, and it alone writes
+// the new ones, after it has read the old: nothing else in the launch touches them.
+template <typename TW>
+__global__ void __launch_bounds__(SC_THREADS) ssd_conv_kernel(const float* __restrict__ proj, long ld, int off,
+                                                              const TW* __restrict__ w, const TW* __restrict__ bias,
+                                                              float* __restrict__ carried, const int* __restrict__ q_start,
+                                                              const int* __restrict__ q_len, const int* __restrict__ slot,
+                                                              float* __restrict__ out, int C, int K) {
+  hb_pdl_launch();
+  hb_pdl_wait();
+  const int c = blockIdx.x * SC_THREADS + threadIdx.x, r = blockIdx.y;
+  const int len = q_len[r], j0 = blockIdx.z * SC_CHUNK;
+  if (c >= C || j0 >= len) return;
+  const int t0 = q_start[r], K1 = K - 1;
+  float* st = carried + (size_t)slot[r] * K1 * C + c;          // [K - 1][C], oldest first
+  float wk[SC_TAPS_MAX], hist[SC_TAPS_MAX], old[SC_TAPS_MAX];
+#pragma unroll
+  for (int k = 0; k < SC_TAPS_MAX; k++) wk[k] = k < K ? hb_to_float(w[(size_t)c * K + k]) : 0.f;
+  const float bs = hb_to_float(bias[c]);
+  const float* in = proj + (size_t)t0 * ld + off + c;
+  // hist[i]: the raw input i + 1 tokens before the current one
+#pragma unroll
+  for (int i = 0; i < SC_TAPS_MAX - 1; i++) {
+    old[i] = (blockIdx.z == 0 && i < K1) ? st[(size_t)i * C] : 0.f;
+    hist[i] = 0.f;
+  }
+#pragma unroll
+  for (int i = 0; i < SC_TAPS_MAX - 1; i++) {
+    if (i < K1) {
+      const int j = j0 - 1 - i;
+      if (j >= 0) hist[i] = in[(size_t)j * ld];
+      else {
+        float v = 0.f;                                         // old[K1 + j], a dynamic index kept out of local memory
+#pragma unroll
+        for (int q = 0; q < SC_TAPS_MAX - 1; q++) v = (q == K1 + j) ? old[q] : v;
+        hist[i] = v;
+      }
+    }
+  }
+  const int n = min(SC_CHUNK, len - j0);
+  for (int j = 0; j < n; j++) {
+    const float cur = in[(size_t)(j0 + j) * ld];
+    float acc = bs;
+#pragma unroll
+    for (int i = SC_TAPS_MAX - 2; i >= 0; i--)
+      if (i < K1) acc = fmaf(wk[K1 - 1 - i], hist[i], acc);    // tap k multiplies the input K - 1 - k tokens back
+    acc = fmaf(wk[K1], cur, acc);
+    out[(size_t)(t0 + j0 + j) * C + c] = acc / (1.f + expf(-acc));
+#pragma unroll
+    for (int i = SC_TAPS_MAX - 2; i > 0; i--) hist[i] = hist[i - 1];
+    hist[0] = cur;
+  }
+  if (blockIdx.z == 0) {
+    for (int k = 0; k < K1; k++) {
+      const int j = len - K1 + k;                              // relative index of the input that becomes carried[k]
+      float v;
+      if (j >= 0) v = in[(size_t)j * ld];
+      else {
+        v = 0.f;
+#pragma unroll
+        for (int q = 0; q < SC_TAPS_MAX - 1; q++) v = (q == K1 + j) ? old[q] : v;
+      }
+      st[(size_t)k * C] = v;
+    }
+  }
+}
+
+HB_EXPORT int hb_ssd_conv(const float* proj, long ld, int off, const void* w, const void* bias, int w_dt, float* carried,
+                          const int* q_start, const int* q_len, const int* slot, float* out, int n_requests, int max_q_len,
+                          int C, int K, cudaStream_t s) {
+  if (n_requests <= 0 || max_q_len <= 0) return 0;
+  if (K < 1 || K > SC_TAPS_MAX) HB_FAIL("hb_ssd_conv: %d taps (1 to %d are supported)", K, SC_TAPS_MAX);
+  dim3 grid((C + SC_THREADS - 1) / SC_THREADS, n_requests, (max_q_len + SC_CHUNK - 1) / SC_CHUNK);
+  if (grid.y > 65535 || grid.z > 65535) HB_FAIL("hb_ssd_conv: the grid is too large");
+  HB_DISPATCH_1(w_dt, "hb_ssd_conv",
+                (hb_launch(ssd_conv_kernel<TA>, grid, dim3(SC_THREADS), 0, s, proj, ld, off, (const TA*)w, (const TA*)bias, carried,
+                           q_start, q_len, slot, out, C, K)));
+  HB_CHECK_LAUNCH("hb_ssd_conv");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// The recurrence. A block owns (head, request) and walks the request's rows of the step in order, from and into its state
+// slot. The state lives in registers: KS threads share a value channel p, thread ks holds the state channels n = i KS + ks.
+// Tokens go by in chunks of SS_CH: a chunk's rows (x of the head, B and C of its group, dt) are asked for a chunk ahead
+// (cp.async), what does not depend on the state (dt, the decay, dt B) is prepared in place, the walk reads it by
+// broadcast.
+// ---------------------------------------------------------------------------------------------------------------------
+constexpr int SS_CH = 16;
+
+struct SsdArgs {
+  const float* xbc; long ldx;            // after the convolution: [T][H P | G N | G N]
+  const float* dt; long lddt;            // raw dt, [T][.. H ..] (already offset to its first column)
+  const void* dt_bias; const void* a_log; const void* d_skip;   // [H] each
+  float* state;                          // [slots][H][N][P]
+  const int* q_start; const int* q_len; const int* slot;
+  float* y;                              // [T][H P]
+  int H, P, N, G, KS, vec4;
+};
+
+__device__ __forceinline__ void ss_cp16(float* dst, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void ss_cp4(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+
+template <int DPT> struct SsdThreads { static constexpr int MAX = DPT <= 8 ? 1024 : DPT <= 32 ? 512 : 256; };
+
+template <int DPT, typename TW>
+__global__ void __launch_bounds__(SsdThreads<DPT>::MAX, 1) ssd_scan_kernel(SsdArgs A) {
+  extern __shared__ __align__(16) float ssm[];
+  hb_pdl_launch();
+  hb_pdl_wait();
+  const int h = blockIdx.x, r = blockIdx.y, tid = threadIdx.x, nthr = blockDim.x;
+  const int H = A.H, P = A.P, N = A.N, KS = A.KS;
+  const int g = h / (H / A.G);
+  const int p = tid / KS, ks = tid - p * KS;
+  const bool live = p < P;
+  const int t0 = A.q_start[r], len = A.q_len[r];
+  float* S_g = A.state + ((size_t)A.slot[r] * H + h) * N * P;
+  // a token's row in shared memory: [B -> dt B (N) | C (N) | x (P) | dt_raw -> decay (1) | pad], two chunks deep
+  const int RW = ((2 * N + P + 1 + 3) / 4) * 4;
+  float S[DPT];
+#pragma unroll
+  for (int i = 0; i < DPT; i++) {
+    const int n = i * KS + ks;
+    S[i] = (live && n < N) ? S_g[(size_t)n * P + p] : 0.f;
+  }
+  const float dtb = hb_to_float(((const TW*)A.dt_bias)[h]);
+  const float neg_a = -expf(hb_to_float(((const TW*)A.a_log)[h]));
+  const float dsk = hb_to_float(((const TW*)A.d_skip)[h]);
+  const int HP = H * P, GN = A.G * N;
+  auto fetch = [&](int buf, int c0) {
+    const int n = min(SS_CH, len - c0);
+    float* st = ssm + buf * SS_CH * RW;
+    if (A.vec4) {
+      const int cn = N >> 2, cp = P >> 2, per = 2 * cn + cp;
+      for (int i = tid; i < n * per; i += nthr) {
+        const int j = i / per, c = i - j * per;
+        const float* row = A.xbc + (size_t)(t0 + c0 + j) * A.ldx;
+        if (c < cn) ss_cp16(st + j * RW + 4 * c, row + HP + g * N + 4 * c);
+        else if (c < 2 * cn) ss_cp16(st + j * RW + N + 4 * (c - cn), row + HP + GN + g * N + 4 * (c - cn));
+        else ss_cp16(st + j * RW + 2 * N + 4 * (c - 2 * cn), row + h * P + 4 * (c - 2 * cn));
+      }
+    } else {
+      const int per = 2 * N + P;
+      for (int i = tid; i < n * per; i += nthr) {
+        const int j = i / per, c = i - j * per;
+        const float* row = A.xbc + (size_t)(t0 + c0 + j) * A.ldx;
+        const float* src = c < N ? row + HP + g * N + c : c < 2 * N ? row + HP + GN + g * N + (c - N) : row + h * P + (c - 2 * N);
+        ss_cp4(st + j * RW + c, src);
+      }
+    }
+    for (int j = tid; j < n; j += nthr) ss_cp4(st + j * RW + 2 * N + P, A.dt + (size_t)(t0 + c0 + j) * A.lddt + h);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  if (len > 0) fetch(0, 0);
+  int buf = 0;
+  for (int c0 = 0; c0 < len; c0 += SS_CH, buf ^= 1) {
+    const int n = min(SS_CH, len - c0);
+    if (c0 + SS_CH < len) {
+      fetch(buf ^ 1, c0 + SS_CH);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    float* st = ssm + buf * SS_CH * RW;
+    // what does not depend on the state: the step size, dt B, and (last, by one thread a token) the decay in dt's place
+    for (int i = tid; i < n * N; i += nthr) {
+      const int j = i / N, c = i - j * N;
+      float* row = st + j * RW;
+      const float zz = row[2 * N + P] + dtb;
+      const float dt = fmaxf(zz, 0.f) + log1pf(expf(-fabsf(zz)));
+      row[c] *= dt;
+    }
+    __syncthreads();
+    for (int j = tid; j < n; j += nthr) {
+      float* row = st + j * RW;
+      const float zz = row[2 * N + P] + dtb;
+      const float dt = fmaxf(zz, 0.f) + log1pf(expf(-fabsf(zz)));
+      row[2 * N + P] = expf(neg_a * dt);
+    }
+    __syncthreads();
+    for (int j = 0; j < n; j++) {
+      const float* row = st + j * RW;
+      const float xv = live ? row[2 * N + p] : 0.f;
+      const float a = row[2 * N + P];
+      const float* Bj = row;
+      const float* Cj = row + N;
+      float o = 0.f, o2 = 0.f;
+#pragma unroll
+      for (int i = 0; i < DPT; i += 2) {
+        const int n0 = i * KS + ks, n1 = n0 + KS;
+        if (n0 < N) {
+          S[i] = fmaf(a, S[i], Bj[n0] * xv);
+          o = fmaf(S[i], Cj[n0], o);
+        }
+        if (n1 < N) {
+          S[i + 1] = fmaf(a, S[i + 1], Bj[n1] * xv);
+          o2 = fmaf(S[i + 1], Cj[n1], o2);
+        }
+      }
+      o += o2;
+      for (int m = 1; m < KS; m <<= 1) o += __shfl_xor_sync(0xffffffffu, o, m);
+      if (live && ks == 0) A.y[(size_t)(t0 + c0 + j) * HP + h * P + p] = fmaf(dsk, xv, o);
+    }
+    __syncthreads();             // the buffer is free for the chunk after the next
+  }
+#pragma unroll
+  for (int i = 0; i < DPT; i++) {
+    const int n = i * KS + ks;
+    if (live && n < N) S_g[(size_t)n * P + p] = S[i];
+  }
+}
+
+HB_EXPORT int hb_ssd_scan(const float* xbc, long ldx, const float* dt, long lddt, const void* dt_bias, const void* a_log,
+                          const void* d_skip, int w_dt, float* state, const int* q_start, const int* q_len, const int* slot,
+                          float* y, int n_requests, int H, int P, int N, int G, cudaStream_t s) {
+  if (n_requests <= 0) return 0;
+  if (P > 1024 || G <= 0 || H % G) HB_FAIL("hb_ssd_scan: %d heads of %d in %d groups", H, P, G);
+  // threads a value channel (a power of two up to 32): the fewest that give the block 256 threads, else the most that fit
+  int ks = 0;
+  for (int c = 1; c <= 32; c *= 2) {
+    const int per_c = (N + c - 1) / c, threads_c = ((P * c + 31) / 32) * 32;
+    if (per_c > 64) continue;
+    const int limit = per_c <= 8 ? 1024 : per_c <= 32 ? 512 : 256;
+    if (threads_c > limit) break;
+    ks = c;
+    if (threads_c >= 256) break;
+  }
+  if (!ks) HB_FAIL("hb_ssd_scan: heads of %d x %d do not fit a block's registers", N, P);
+  const int per = (N + ks - 1) / ks;
+  SsdArgs A;
+  A.xbc = xbc; A.ldx = ldx; A.dt = dt; A.lddt = lddt; A.dt_bias = dt_bias; A.a_log = a_log; A.d_skip = d_skip; A.state = state;
+  A.q_start = q_start; A.q_len = q_len; A.slot = slot; A.y = y; A.H = H; A.P = P; A.N = N; A.G = G; A.KS = ks;
+  A.vec4 = !((N | P) & 3) && !(ldx & 3) && !((uintptr_t)xbc & 15);
+  const int threads = ((P * ks + 31) / 32) * 32;
+  const int RW = ((2 * N + P + 1 + 3) / 4) * 4;
+  const size_t smem = (size_t)2 * SS_CH * RW * sizeof(float);
+  if (smem > 200 * 1024) HB_FAIL("hb_ssd_scan: heads of %d x %d do not fit shared memory", N, P);
+  dim3 grid(H, n_requests);
+#define SS_LAUNCH(DPT)                                                                                             \
+  HB_DISPATCH_1(w_dt, "hb_ssd_scan", do {                                                                          \
+    auto kern = ssd_scan_kernel<DPT, TA>;                                                                          \
+    if (smem + 4096 > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
+    hb_launch(kern, grid, dim3(threads), smem, s, A);                                                              \
+  } while (0))
+  if (per <= 8) SS_LAUNCH(8);
+  else if (per <= 16) SS_LAUNCH(16);
+  else if (per <= 32) SS_LAUNCH(32);
+  else SS_LAUNCH(64);
+#undef SS_LAUNCH
+  HB_CHECK_LAUNCH("hb_ssd_scan");
+  return 0;
+}
+
+// One block a row: y silu(z), then every part of the row by its own root mean square, times the weight.
+template <typename TW, typename TO>
+__global__ void __launch_bounds__(256) ssd_gate_norm_kernel(const float* __restrict__ y, const float* __restrict__ z, long ldz,
+                                                            const TW* __restrict__ w, TO* __restrict__ out, int inner,
+                                                            int parts, float eps) {
+  __shared__ float sh[32];
+  hb_pdl_launch();
+  hb_pdl_wait();
+  const int t = blockIdx.x, span = inner / parts;
+  const float* yr = y + (size_t)t * inner;
+  const float* zr = z + (size_t)t * ldz;
+  for (int q = 0; q < parts; q++) {
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < span; i += 256) {
+      const float zz = zr[q * span + i], v = yr[q * span + i] * (zz / (1.f + expf(-zz)));
+      ss = fmaf(v, v, ss);
+    }
+    const float f = rsqrtf(hb_block_sum(ss, sh) / (float)span + eps);
+    for (int i = threadIdx.x; i < span; i += 256) {
+      const float zz = zr[q * span + i], v = yr[q * span + i] * (zz / (1.f + expf(-zz)));
+      out[(size_t)t * inner + q * span + i] = hb_from_float<TO>(v * f * hb_to_float(w[q * span + i]));
+    }
+  }
+}
+
+HB_EXPORT int hb_ssd_gate_norm(const float* y, const float* z, long ldz, const void* w, int w_dt, void* out, int o_dt, int T,
+                               int inner, int parts, float eps, cudaStream_t s) {
+  if (T <= 0) return 0;
+  if (parts <= 0 || inner % parts) HB_FAIL("hb_ssd_gate_norm: %d channels in %d parts", inner, parts);
+  HB_DISPATCH_2(w_dt, o_dt, "hb_ssd_gate_norm",
+                (hb_launch(ssd_gate_norm_kernel<TA, TB>, T, 256, 0, s, y, z, ldz, (const TA*)w, (TB*)out, inner, parts, eps)));
+  HB_CHECK_LAUNCH("hb_ssd_gate_norm");
+  return 0;
+}

@@ -56,6 +56,24 @@ _SIGS = {
                                  _i, _l, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _p],
         "hb_gla": [_p, _l, _i, _i, _i, _i, _p, _l, _p, _p, _i, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _f, _f, _p],
     },
+    "hybrid": {
+        "hb_streams_norm": [_p, _p, _i, _p, _p, _i, _p, _i, _i, _i, _f, _p],
+        "hb_streams_update": [_p, _p, _p, _p, _f, _i, _i, _i, _p],
+        "hb_streams_update_norm": [_p, _p, _p, _p, _f, _p, _p, _i, _p, _i, _i, _i, _i, _f, _p],
+        "hb_streams_expand": [_p, _p, _i, _i, _i, _p],
+        "hb_glu_bias": [_p, _l, _p, _i, _p, _i, _l, _i, _i, _i, _i, _f, _f, _p],
+        "hb_scale_bias_rows": [_p, _l, _p, _i, _f, _i, _i, _p],
+        "hb_ssd_conv": [_p, _l, _i, _p, _p, _i, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p],
+        "hb_ssd_scan": [_p, _l, _p, _l, _p, _p, _p, _i, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p],
+        "hb_ssd_gate_norm": [_p, _p, _l, _p, _i, _p, _i, _i, _i, _i, _f, _p],
+        "hb_moe_route": [_p, _i, _l, _p, _i, _p, _p, _i, _i, _i, _i, _p],
+        "hb_moe_gate_up_rows": [_p, _i, _l, _p, _i, _p, _p, _p, _i, _i, _i, _i, _p],
+        "hb_moe_down_rows": [_p, _i, _p, _i, _p, _p, _l, _i, _i, _i, _i, _p],
+        "hb_moe_sort": [_p, _p, _p, _p, _i, _i, _p],
+        "hb_moe_gather": [_p, _i, _l, _p, _p, _i, _i, _i, _p],
+        "hb_moe_act": [_p, _p, _p, _p, _i, _i, _i, _p],
+        "hb_moe_combine": [_p, _p, _p, _l, _i, _i, _i, _p],
+    },
     "mixers": {
         "hb_delta_rule": [_p, _l, _i, _i, _i, _i, _i, _p, _l, _p, _p, _p, _i, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _f, _f,
                           _i, _p],
@@ -883,11 +901,11 @@ def latent_prepare(proj: torch.Tensor, offsets, wq: torch.Tensor, wc: torch.Tens
     _rows_contiguous(proj, "latent_prepare in")
     T = proj.shape[0]
     assert proj.dtype == torch.float32 and cq_out.is_contiguous() and cq_out.shape == (T, q_rank)
-    assert wq.dtype == wc.dtype and wq.numel() == q_rank and wc.numel() == kv_rank
+    assert wc.numel() == kv_rank and ((wq is None and q_rank == 0) or (wq.dtype == wc.dtype and wq.numel() == q_rank))
     if slot_map is not None:
         assert cache.is_contiguous() and cache.dtype == cq_out.dtype and cache.shape[1] == 1 and cache.shape[-1] == kv_rank + rot_dim
     a, b, c = (int(o) for o in offsets)
-    _call("seqmix", "hb_latent_prepare", proj.data_ptr(), proj.stride(0), a, b, c, wq.data_ptr(), wc.data_ptr(), _dt(wq),
+    _call("seqmix", "hb_latent_prepare", proj.data_ptr(), proj.stride(0), a, b, c, _ptr(wq), wc.data_ptr(), _dt(wc),
           positions.data_ptr(), _ptr(slot_map), table.data_ptr(), int(rot), float(eps), cq_out.data_ptr(),
           _ptr(cache) if slot_map is not None else None, _dt(cq_out), T, q_rank, kv_rank, rot_dim, page_size, _stream())
     return cq_out
@@ -949,18 +967,22 @@ def masked_flash_supported(dim: int, vdim: int) -> bool:
 
 
 def attention_flash_tokens(q, keys, values, batch, request: int, out, n_heads: int, n_kv_heads: int, dim: int, vdim: int,
-                           scale: float, gate=None, gate_offset: int = 0, gate_per_head: bool = False) -> torch.Tensor:
-    """Causal attention of the rows of ONE request of the batch (index `request`) over keys and values made for its whole
+                           scale: float, gate=None, gate_offset: int = 0, gate_per_head: bool = False, window: int = 0,
+                           first_pos: int = 0) -> torch.Tensor:
+    """Causal attention of the rows of ONE request of the batch (index `request`) over keys and values made for its
     context in token-major buffers: keys [n, >= n_kv_heads * dim] and values [n, >= n_kv_heads * vdim] (views of wider
-    rows are fine), row t the token at position t. bfloat16; the tensor-core kernel of csrc/attention_masked_flash.cu."""
+    rows are fine), row t the token at position first_pos + t. With `window` a row at position i sees the keys j with
+    0 <= i - j < window (first_pos must not lie behind the first key that the request's first row sees). bfloat16; the
+    tensor-core kernel of csrc/attention_masked_flash.cu."""
     _need_cuda(q, keys, values, out, gate)
     n = keys.shape[0]
     assert q.dtype == keys.dtype == values.dtype == torch.bfloat16 and keys.stride(1) == values.stride(1) == 1
     _call("seqmix", "hb_attn_masked_flash", q.data_ptr(), q.stride(0), keys.data_ptr(), keys.stride(0), dim, 0, values.data_ptr(),
-          values.stride(0), vdim, 0, _identity_table(q.device, n).data_ptr(), 0, batch.req_q_start.data_ptr(),
+          values.stride(0), vdim, 0, _identity_table(q.device, n).data_ptr() - 4 * int(first_pos), 0, batch.req_q_start.data_ptr(),
           batch.req_q_len.data_ptr(), batch.req_ctx_len.data_ptr(), int(request), 1, int(batch.h_q_len[request]), 1, None,
           _ptr(gate), gate.stride(0) if gate is not None else 0, int(gate_offset), (2 if gate_per_head else 1) if gate is not None else 0,
-          out.data_ptr(), _dt(out), out.stride(0), n_heads, n_kv_heads, dim, vdim, 1, 0, 0, 0, 0, float(scale), _stream())
+          out.data_ptr(), _dt(out), out.stride(0), n_heads, n_kv_heads, dim, vdim, 1, 1 if window else 0, int(window), 0, 0,
+          float(scale), _stream())
     return out
 
 
@@ -981,3 +1003,202 @@ def gla(proj: torch.Tensor, offsets, z: torch.Tensor, a_bias, norm_weight, state
           batch.req_state_slot.data_ptr(), out.data_ptr(), _dt(out), batch.n_requests, heads, dim, vdim, float(tau),
           float(eps), _stream())
     return out
+
+
+# ------------------------------------------------------------------------------------------
+# The `hybrid` library: residual streams with learned mixing, the state-space recurrence with a scalar decay per head,
+# routed feed-forward layers, a gated activation with biases and limits
+# ------------------------------------------------------------------------------------------
+def streams_norm(x: torch.Tensor, read: Optional[torch.Tensor], weight: torch.Tensor, eps: float, out: torch.Tensor,
+                 streams: int, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out = rms norm of u = sum_s read[s] x_s (read None: the plain sum) times weight, for the residual rows x float32
+    [T, streams * W]; with `rows` (int32 on the device) of those rows only."""
+    _need_cuda(x, read, weight, out, rows)
+    W = weight.numel()
+    n = x.shape[0] if rows is None else rows.numel()
+    assert x.dtype == torch.float32 and x.is_contiguous() and x.shape[1] == streams * W and out.is_contiguous()
+    assert out.shape == (n, W) and (read is None or (read.dtype == torch.float32 and read.numel() == streams))
+    _call("hybrid", "hb_streams_norm", x.data_ptr(), _ptr(rows), n, _ptr(read), weight.data_ptr(), _dt(weight), out.data_ptr(),
+          _dt(out), int(streams), W, float(eps), _stream())
+    return out
+
+
+def streams_update(x: torch.Tensor, y: torch.Tensor, write: Optional[torch.Tensor], mix: Optional[torch.Tensor], mult: float,
+                   streams: int, next_read: Optional[torch.Tensor] = None, next_weight: Optional[torch.Tensor] = None,
+                   eps: float = 0.0, out: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """x_t <- sum_s mix[s, t] x_s + mult * write[t] * y for all streams t at once (write None: ones; mix None: the
+    identity), x float32 [T, streams * W], y float32 [T, W]. With next_weight (and `out`): also the norm of the sublayer
+    that reads x next, out = rms norm of sum_s next_read[s] x_s times next_weight, in the same pass over the row."""
+    _need_cuda(x, y, write, mix, next_read, next_weight, out)
+    T, W = y.shape
+    assert x.dtype == y.dtype == torch.float32 and x.is_contiguous() and y.is_contiguous() and x.shape == (T, streams * W)
+    for c, n in ((write, streams), (mix, streams * streams), (next_read, streams)):
+        assert c is None or (c.dtype == torch.float32 and c.is_contiguous() and c.numel() == n)
+    if next_weight is None:
+        _call("hybrid", "hb_streams_update", x.data_ptr(), y.data_ptr(), _ptr(write), _ptr(mix), float(mult), T, int(streams), W,
+              _stream())
+        return None
+    assert out.is_contiguous() and out.shape == (T, W) and next_weight.numel() == W
+    _call("hybrid", "hb_streams_update_norm", x.data_ptr(), y.data_ptr(), _ptr(write), _ptr(mix), float(mult), _ptr(next_read),
+          next_weight.data_ptr(), _dt(next_weight), out.data_ptr(), _dt(out), T, int(streams), W, float(eps), _stream())
+    return out
+
+
+def streams_expand(x: torch.Tensor, xs: torch.Tensor, streams: int) -> torch.Tensor:
+    """xs [T, streams * W] = `streams` copies of every row of x [T, W] (float32)."""
+    _need_cuda(x, xs)
+    T, W = x.shape
+    assert x.dtype == xs.dtype == torch.float32 and x.is_contiguous() and xs.is_contiguous() and xs.shape == (T, streams * W)
+    _call("hybrid", "hb_streams_expand", x.data_ptr(), xs.data_ptr(), T, int(streams), W, _stream())
+    return xs
+
+
+GLU_KINDS = {"silu": 0, "gelu_tanh": 1, "clamped_sigmoid": 2}
+
+
+def glu_bias(gate_up: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, group: int, kind: str,
+             limit: float = 0.0, alpha: float = 1.0) -> torch.Tensor:
+    """out[m, i] = the gated activation of a float32 gate/up matrix [M, 2I] interleaved in groups of `group` columns,
+    after adding `bias` [2I] (same order). kind "silu" / "gelu_tanh": act(g) * u; "clamped_sigmoid": g' = min(g, limit),
+    u' = clamp(u, -limit, limit), out = g' sigmoid(alpha g') (u' + 1)."""
+    _need_cuda(gate_up, bias, out)
+    _rows_contiguous(gate_up, "glu_bias in")
+    _rows_contiguous(out, "glu_bias out")
+    M, I = out.shape
+    assert gate_up.dtype == torch.float32 and gate_up.shape == (M, 2 * I) and (bias is None or bias.numel() == 2 * I)
+    _call("hybrid", "hb_glu_bias", gate_up.data_ptr(), gate_up.stride(0), _ptr(bias), _dt(bias) if bias is not None else 0,
+          out.data_ptr(), _dt(out), out.stride(0), M, I, int(group), GLU_KINDS[kind], float(limit), float(alpha), _stream())
+    return out
+
+
+def scale_bias_rows(x: torch.Tensor, scale: float = 1.0, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x[m, n] = x[m, n] * scale + bias[n] in place on float32 rows (bias None: the scale alone)."""
+    _need_cuda(x, bias)
+    _rows_contiguous(x, "scale_bias_rows")
+    assert x.dtype == torch.float32 and (bias is None or bias.numel() == x.shape[1])
+    _call("hybrid", "hb_scale_bias_rows", x.data_ptr(), x.stride(0), _ptr(bias), _dt(bias) if bias is not None else 0,
+          float(scale), x.shape[0], x.shape[1], _stream())
+    return x
+
+
+def ssd_conv(proj: torch.Tensor, offset: int, weight: torch.Tensor, bias: torch.Tensor, carried: torch.Tensor, batch,
+             out: torch.Tensor) -> torch.Tensor:
+    """out [T, C] = silu(causal convolution over each request's tokens + bias) of the C columns of the float32 rows `proj`
+    from `offset` on; weight [C, K] (its last column multiplies the current token), zeros before a sequence. carried
+    float32 [slots, K - 1, C] holds each request's last K - 1 raw inputs between steps and is brought up to date."""
+    _need_cuda(proj, weight, bias, carried, out)
+    _rows_contiguous(proj, "ssd_conv in")
+    C, K = weight.shape
+    assert proj.dtype == out.dtype == carried.dtype == torch.float32 and out.is_contiguous() and out.shape == (proj.shape[0], C)
+    assert weight.is_contiguous() and weight.dtype == bias.dtype and bias.numel() == C and carried.is_contiguous()
+    assert carried.shape[1:] == (K - 1, C)
+    _call("hybrid", "hb_ssd_conv", proj.data_ptr(), proj.stride(0), int(offset), weight.data_ptr(), bias.data_ptr(), _dt(weight),
+          carried.data_ptr() if carried.numel() else None, batch.req_q_start.data_ptr(), batch.req_q_len.data_ptr(),
+          batch.req_state_slot.data_ptr(), out.data_ptr(), batch.n_requests, batch.max_q_len, C, K, _stream())
+    return out
+
+
+def ssd_scan(xbc: torch.Tensor, dt: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor, d_skip: torch.Tensor,
+             state: torch.Tensor, batch, y: torch.Tensor, heads: int, vdim: int, n_state: int, groups: int) -> torch.Tensor:
+    """The state-space recurrence with a scalar decay per head over the step's rows, request by request, from and into
+    each request's state slot (csrc/ssd.cu). xbc float32 [T, heads * vdim | groups * n_state | groups * n_state] (x, B, C
+    after the convolution), dt float32 [T, heads] raw (a view of wider rows is fine), state float32
+    [slots, heads, n_state, vdim], y float32 [T, heads * vdim]."""
+    _need_cuda(xbc, dt, dt_bias, a_log, d_skip, state, y)
+    _rows_contiguous(xbc, "ssd_scan xbc")
+    _rows_contiguous(dt, "ssd_scan dt")
+    T = xbc.shape[0]
+    assert xbc.dtype == dt.dtype == state.dtype == y.dtype == torch.float32 and state.is_contiguous() and y.is_contiguous()
+    assert xbc.shape[1] == heads * vdim + 2 * groups * n_state and dt.shape == (T, heads) and y.shape == (T, heads * vdim)
+    assert state.shape[1:] == (heads, n_state, vdim) and dt_bias.dtype == a_log.dtype == d_skip.dtype
+    assert dt_bias.numel() == a_log.numel() == d_skip.numel() == heads
+    _call("hybrid", "hb_ssd_scan", xbc.data_ptr(), xbc.stride(0), dt.data_ptr(), dt.stride(0), dt_bias.data_ptr(),
+          a_log.data_ptr(), d_skip.data_ptr(), _dt(dt_bias), state.data_ptr(), batch.req_q_start.data_ptr(),
+          batch.req_q_len.data_ptr(), batch.req_state_slot.data_ptr(), y.data_ptr(), batch.n_requests, heads, vdim, n_state,
+          groups, _stream())
+    return y
+
+
+def ssd_gate_norm(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, parts: int, eps: float) -> torch.Tensor:
+    """out = (y * silu(z)) with each of the row's `parts` equal parts divided by its own root mean square (eps inside the
+    root), times weight; y float32 [T, inner], z float32 [T, inner] (a view of wider rows is fine)."""
+    _need_cuda(y, z, weight, out)
+    _rows_contiguous(z, "ssd_gate_norm z")
+    T, inner = y.shape
+    assert y.dtype == z.dtype == torch.float32 and y.is_contiguous() and out.is_contiguous() and out.shape == (T, inner)
+    assert weight.numel() == inner and z.shape == (T, inner)
+    _call("hybrid", "hb_ssd_gate_norm", y.data_ptr(), z.data_ptr(), z.stride(0), weight.data_ptr(), _dt(weight), out.data_ptr(),
+          _dt(out), T, inner, int(parts), float(eps), _stream())
+    return out
+
+
+def moe_route(xn: torch.Tensor, router: torch.Tensor, top: int):
+    """(expert int32 [T, top], score float32 [T, top]): the `top` experts with the largest sigmoid(router @ row), 32-bit
+    sums; the largest first, ties to the lower index."""
+    _need_cuda(xn, router)
+    _rows_contiguous(xn, "moe_route in")
+    T, (E, W) = xn.shape[0], router.shape
+    assert router.is_contiguous() and xn.shape[1] == W
+    expert = torch.empty(T, top, dtype=torch.int32, device=xn.device)
+    score = torch.empty(T, top, dtype=torch.float32, device=xn.device)
+    _call("hybrid", "hb_moe_route", xn.data_ptr(), _dt(xn), xn.stride(0), router.data_ptr(), _dt(router), expert.data_ptr(),
+          score.data_ptr(), T, W, E, int(top), _stream())
+    return expert, score
+
+
+def moe_rows(xn: torch.Tensor, wgu: torch.Tensor, wdown: torch.Tensor, expert: torch.Tensor, score: torch.Tensor,
+             y: torch.Tensor) -> torch.Tensor:
+    """y += sum over a row's chosen experts of Wd_e (silu(s Wg_e h) * (s Wu_e h)), row by row with nothing sorted and
+    nothing on the host. wgu [E, 2F, W] (gate rows, then up rows), wdown [E, W, F], y float32 [T, W]."""
+    _need_cuda(xn, wgu, wdown, expert, score, y)
+    _rows_contiguous(xn, "moe_rows in")
+    _rows_contiguous(y, "moe_rows out")
+    T, top = expert.shape
+    E, F2, W = wgu.shape
+    F = F2 // 2
+    assert wgu.is_contiguous() and wdown.is_contiguous() and wdown.shape == (E, W, F) and y.dtype == torch.float32
+    act = torch.empty(T * top, F, dtype=xn.dtype, device=xn.device)
+    _call("hybrid", "hb_moe_gate_up_rows", xn.data_ptr(), _dt(xn), xn.stride(0), wgu.data_ptr(), _dt(wgu), expert.data_ptr(),
+          score.data_ptr(), act.data_ptr(), T, W, F, top, _stream())
+    _call("hybrid", "hb_moe_down_rows", act.data_ptr(), _dt(act), wdown.data_ptr(), _dt(wdown), expert.data_ptr(), y.data_ptr(),
+          y.stride(0), T, W, F, top, _stream())
+    return y
+
+
+def moe_sort(expert: torch.Tensor, n_experts: int):
+    """The (row, choice) pairs sorted by expert: offsets int32 [E + 1] (first sorted row of each expert), pos int32 [pairs]
+    (the sorted row of a pair), src int32 [pairs] (the pair of a sorted row)."""
+    pairs = expert.numel()
+    dev = expert.device
+    offsets = torch.empty(n_experts + 1, dtype=torch.int32, device=dev)
+    pos = torch.empty(pairs, dtype=torch.int32, device=dev)
+    src = torch.empty(pairs, dtype=torch.int32, device=dev)
+    _call("hybrid", "hb_moe_sort", expert.data_ptr(), offsets.data_ptr(), pos.data_ptr(), src.data_ptr(), pairs, int(n_experts),
+          _stream())
+    return offsets, pos, src
+
+
+def moe_gather(xn: torch.Tensor, src: torch.Tensor, top: int) -> torch.Tensor:
+    """The input rows in sorted order: out[r] = xn[src[r] // top]."""
+    _rows_contiguous(xn, "moe_gather in")
+    out = torch.empty(src.numel(), xn.shape[1], dtype=xn.dtype, device=xn.device)
+    _call("hybrid", "hb_moe_gather", xn.data_ptr(), _dt(xn), xn.stride(0), src.data_ptr(), out.data_ptr(), src.numel(),
+          xn.shape[1], int(top), _stream())
+    return out
+
+
+def moe_act(gu: torch.Tensor, src: torch.Tensor, score: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[r] = silu(s g) * (s u) of the sorted rows' float32 [g | u], s the score of the row's pair."""
+    pairs, F = out.shape
+    assert gu.dtype == torch.float32 and gu.is_contiguous() and gu.shape == (pairs, 2 * F) and out.is_contiguous()
+    _call("hybrid", "hb_moe_act", gu.data_ptr(), src.data_ptr(), score.data_ptr(), out.data_ptr(), _dt(out), pairs, F, _stream())
+    return out
+
+
+def moe_combine(ys: torch.Tensor, pos: torch.Tensor, y: torch.Tensor, top: int) -> torch.Tensor:
+    """y[t] += the sorted results of row t's choices, added in the order of the choices."""
+    _rows_contiguous(y, "moe_combine out")
+    T, W = y.shape
+    assert ys.dtype == y.dtype == torch.float32 and ys.is_contiguous() and ys.shape == (T * top, W)
+    _call("hybrid", "hb_moe_combine", ys.data_ptr(), pos.data_ptr(), y.data_ptr(), y.stride(0), T, W, int(top), _stream())
+    return y

@@ -217,6 +217,112 @@ class ParallelBlock(Part):
         return None
 
 
+class PreparedNorm:
+    """The rows of `norm` over the residual rows as a layer left them: the layer's last write-back computed them on its
+    way, so the layer that owns `norm` need not read the residual rows again."""
+
+    def __init__(self, norm, rows):
+        self.norm, self.rows = norm, rows
+
+
+class HyperConnectionBlock(Part):
+    """Pre-norm sublayers over several residual streams with learned mixing (hyper-connections). A token's residual row
+    holds S streams x_1 .. x_S (all equal to the embedding at the start). For each sublayer (the mixer, then the
+    feed-forward where the layer has one), with read weights a [S], write weights b [S], a mixing matrix M [S, S]
+    (indexed [from, to]) and the model's residual multiplier m:
+
+        u = sum_s a[s] x_s;  y = sublayer(norm(u));  x_t <- sum_s M[s, t] x_s + m * b[t] * y   for all t at once
+
+    The read is part of the sublayer's norm (kind "streams_rmsnorm" with a `read_name`); the write-back of a sublayer and
+    the read and norm of the next one are one pass over the row (also across layers: `next_norm`). With S = 1 and no
+    learned weights this is the plain pre-norm residual x <- x + m * sublayer(norm(x)).
+
+    params: layer (the LayerSpec), hidden_size, streams, residual_mult (default 1), learned (default True: the layer has
+    the tensors below), mixer_write_name / mixer_mix_name / feed_forward_write_name / feed_forward_mix_name (defaults
+    "hc1.out", "hc1.mix", "hc2.out", "hc2.mix", relative to the prefix)."""
+
+    SLOTS = {"mixer_norm": "norm", "mixer": "mixer", "feed_forward_norm": "norm", "feed_forward": "feed_forward"}
+    OPTIONAL = ("feed_forward_norm", "feed_forward")
+    takes_pending = True
+    takes_next_norm = True
+
+    def __init__(self, params, ctx, prefix=""):
+        super().__init__(params, ctx, prefix)
+        layer = params["layer"]
+        self.has_ff = "feed_forward" in layer.parts
+        slots = {n: r for n, r in self.SLOTS.items() if self.has_ff or n not in self.OPTIONAL}
+        self.parts = build_slots(self, layer, slots, ctx, prefix)
+        if not self.has_ff:
+            self.feed_forward = self.feed_forward_norm = None
+        self.hidden, self.streams = int(params["hidden_size"]), int(params.get("streams", 1))
+        self.mult, self.learned = float(params.get("residual_mult", 1.0)), bool(params.get("learned", True))
+        subs = ["mixer"] + (["feed_forward"] if self.has_ff else [])
+        dflt = dict(mixer_write="hc1.out", mixer_mix="hc1.mix", feed_forward_write="hc2.out", feed_forward_mix="hc2.mix")
+        self.names = {k: prefix + params.get(k + "_name", d) for k, d in dflt.items() if k.rsplit("_", 1)[0] in subs}
+        self.coef = {}
+
+    def param_specs(self):
+        specs = [s for p in self.parts for s in p.param_specs()]
+        if self.learned:
+            S = self.streams
+            specs += [ParamSpec(n, (S,) if k.endswith("write") else (S, S), init="ones") for k, n in self.names.items()]
+        return specs
+
+    def load(self, tensors):
+        for p in self.parts:
+            p.load(tensors)
+        if self.learned:
+            self.coef = {k: tensors[n].to(torch.float32).contiguous() for k, n in self.names.items()}
+
+    def weight_bytes(self):
+        return sum(p.weight_bytes() for p in self.parts)
+
+    def _write(self, x, y, sub, next_norm):
+        """The write-back of sublayer `sub`; with a `next_norm` of the streams kind also its rows (else None)."""
+        b, M = self.coef.get(sub + "_write"), self.coef.get(sub + "_mix")
+        fuse = (next_norm is not None and getattr(next_norm, "streams", None) == self.streams
+                and getattr(next_norm, "size", None) == self.hidden and hasattr(next_norm, "read")
+                and getattr(next_norm, "weight", None) is not None)
+        if not fuse:
+            ops.streams_update(x, y, b, M, self.mult, self.streams)
+            return None
+        out = torch.empty(y.shape[0], self.hidden, dtype=self.ctx.dtype, device=y.device)
+        return ops.streams_update(x, y, b, M, self.mult, self.streams, next_norm.read, next_norm.weight, next_norm.eps, out)
+
+    def forward(self, x, batch, cache, state, pending=None, next_norm=None):
+        dumping = planes.dumping(batch)
+        if isinstance(pending, ops.Pending):
+            pending.finish()
+        if isinstance(pending, PreparedNorm) and pending.norm is self.mixer_norm and not dumping:
+            xn = pending.rows
+        else:
+            xn = self.mixer_norm.forward(x)
+        planes.record(batch, "mixer_norm", xn)
+        y = torch.zeros(xn.shape[0], self.hidden, dtype=torch.float32, device=xn.device)
+        left = self.mixer.forward(xn, y, batch, cache, state)
+        if isinstance(left, ops.Pending):
+            left.finish()
+        if dumping:
+            next_norm = None
+        if self.has_ff:
+            xn = self._write(x, y, "mixer", None if dumping else self.feed_forward_norm)
+            planes.record(batch, "after_mixer", x)
+            if xn is None:
+                xn = self.feed_forward_norm.forward(x)
+            planes.record(batch, "feed_forward_norm", xn)
+            y = torch.zeros(xn.shape[0], self.hidden, dtype=torch.float32, device=xn.device)
+            left = self.feed_forward.forward(xn, y, batch)
+            if isinstance(left, ops.Pending):
+                left.finish()
+            rows = self._write(x, y, "feed_forward", next_norm)
+        else:
+            rows = self._write(x, y, "mixer", next_norm)
+            planes.record(batch, "after_mixer", x)
+        planes.record(batch, "after_feed_forward", x)
+        return PreparedNorm(next_norm, rows) if rows is not None else None
+
+
 register_part("block", "pre_norm", PreNormBlock)
 register_part("block", "parallel", ParallelBlock)
 register_part("block", "pre_norm_scaled", ScaledPreNormBlock)
+register_part("block", "hyper_connections", HyperConnectionBlock)

@@ -84,14 +84,41 @@ class NormedTokenEmbedding(Part):
         return self.norm.forward(raw, out=torch.empty_like(raw))
 
 
+class StreamsTokenEmbedding(Part):
+    """A token embedding into `streams` residual streams: every token's row of the 32-bit stream tensor holds `streams`
+    copies of its embedding, [T, streams * hidden_size]. params: name, vocab_size, hidden_size, streams."""
+
+    def __init__(self, params, ctx, prefix=""):
+        super().__init__(params, ctx, prefix)
+        self.name, self.vocab, self.hidden = params["name"], int(params["vocab_size"]), int(params["hidden_size"])
+        self.streams = int(params["streams"])
+        self.table = None
+
+    def param_specs(self):
+        return [ParamSpec(self.name, (self.vocab, self.hidden))]
+
+    def load(self, tensors):
+        self.table = to_compute(tensors[self.name], self.ctx)
+
+    def forward(self, tokens):
+        x = torch.empty(tokens.numel(), self.hidden, dtype=torch.float32, device=tokens.device)
+        ops.embedding(self.table, tokens, x)
+        if self.streams == 1:
+            return x
+        return ops.streams_expand(x, torch.empty(tokens.numel(), self.streams * self.hidden, dtype=torch.float32,
+                                                 device=tokens.device), self.streams)
+
+
 class LMHead(Part):
-    """params: name (its own tensor) or tied_to (the embedding's tensor name), vocab_size, hidden_size."""
+    """params: name (its own tensor) or tied_to (the embedding's tensor name), vocab_size, hidden_size, scale (multiplies
+    the 32-bit logits; default 1)."""
 
     def __init__(self, params, ctx, prefix=""):
         super().__init__(params, ctx, prefix)
         self.tied = params.get("tied_to")
         self.name = self.tied or params["name"]
         self.vocab, self.hidden = int(params["vocab_size"]), int(params["hidden_size"])
+        self.scale = float(params.get("scale", 1.0))
         self.weight = None
 
     def param_specs(self):
@@ -107,10 +134,13 @@ class LMHead(Part):
         logits = torch.empty(xn.shape[0], self.vocab, dtype=torch.float32, device=xn.device)
         if xn.shape[0]:
             ops.linear(xn, self.weight, logits)
+            if self.scale != 1.0:
+                ops.scale_bias_rows(logits, self.scale)
         return logits
 
 
 register_part("embedding", "token", TokenEmbedding)
 register_part("embedding", "token_position", ScaledPositionEmbedding)
 register_part("embedding", "token_normed", NormedTokenEmbedding)
+register_part("embedding", "token_streams", StreamsTokenEmbedding)
 register_part("head", "linear", LMHead)

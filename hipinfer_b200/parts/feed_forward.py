@@ -150,6 +150,59 @@ class PolyNormFF(Part):
         return None
 
 
+class ClampedGLU(Part):
+    """A gated dense feed-forward with biases and limits:
+
+        g = min(Wgate h + bg, L);  u = clamp(Wup h + bu, -L, L);  out = Wdown (g sigmoid(alpha g) (u + 1)) + bd
+
+    Gate and up are one product; its 32-bit result takes the biases, the limits and the activation in one kernel, rounded
+    once. Any intermediate size (rows interleaved in groups of 16 where the size allows, else gate rows first).
+
+    params: hidden_size, intermediate_size, limit, alpha (default 1.702), gate_name, up_name, down_name; a projection's
+    bias is its name + ".b"."""
+
+    def __init__(self, params, ctx, prefix=""):
+        super().__init__(params, ctx, prefix)
+        self.hidden, self.inter = int(params["hidden_size"]), int(params["intermediate_size"])
+        self.limit, self.alpha = float(params["limit"]), float(params.get("alpha", 1.702))
+        self.group = GROUP if self.inter % GROUP == 0 else self.inter
+        self.names = {k: prefix + params.get(k + "_name", f"mlp.{k}") for k in ("gate", "up", "down")}
+        self.wgu = self.wdown = self.bgu = self.bdown = None
+
+    def param_specs(self):
+        n, I, H = self.names, self.inter, self.hidden
+        return [ParamSpec(n["gate"], (I, H)), ParamSpec(n["gate"] + ".b", (I,), init="zeros"),
+                ParamSpec(n["up"], (I, H)), ParamSpec(n["up"] + ".b", (I,), init="zeros"),
+                ParamSpec(n["down"], (H, I)), ParamSpec(n["down"] + ".b", (H,), init="zeros")]
+
+    def load(self, tensors):
+        t = lambda name: to_compute(tensors[name], self.ctx)
+        g, u = t(self.names["gate"]), t(self.names["up"])
+        dt = g.dtype if g.dtype == u.dtype else torch.float32
+        I, H, G = self.inter, self.hidden, self.group
+        gu = torch.stack([g.to(dt).reshape(I // G, G, H), u.to(dt).reshape(I // G, G, H)], 1)
+        self.wgu = ops.Weight(gu.reshape(2 * I, H).contiguous())
+        bg, bu = t(self.names["gate"] + ".b"), t(self.names["up"] + ".b")
+        self.bgu = torch.stack([bg.to(dt).reshape(I // G, G), bu.to(dt).reshape(I // G, G)], 1).reshape(2 * I).contiguous()
+        self.wdown = ops.Weight(t(self.names["down"]))
+        self.bdown = t(self.names["down"] + ".b")
+
+    def weight_bytes(self):
+        return self.wgu.nbytes + self.wdown.nbytes + sum(b.numel() * b.element_size() for b in (self.bgu, self.bdown))
+
+    def forward(self, xn, x, batch):
+        T = xn.shape[0]
+        gu = torch.empty(T, 2 * self.inter, dtype=torch.float32, device=xn.device)
+        ops.linear_rows32(xn, self.wgu, gu)
+        act = torch.empty(T, self.inter, dtype=self.ctx.dtype, device=xn.device)
+        ops.glu_bias(gu, self.bgu, act, self.group, "clamped_sigmoid", self.limit, self.alpha)
+        planes.record(batch, "activation", act)
+        ops.linear_into_stream(act, self.wdown, x)
+        ops.scale_bias_rows(x, 1.0, self.bdown)
+        return None
+
+
 register_part("feed_forward", "swiglu", SwiGLU)
 register_part("feed_forward", "polynorm", PolyNormFF)
 register_part("feed_forward", "gated", GatedFF)
+register_part("feed_forward", "clamped_glu", ClampedGLU)

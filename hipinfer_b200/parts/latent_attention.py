@@ -20,8 +20,14 @@ per (row, key) pair: its latents, context and portion, are gathered from the pag
 identity block), and its rows attend over them with queries [plain | rotated] on the tensor-core kernel of
 csrc/attention_masked_flash.cu, the gate in its epilogue. Both ways compute the same sums; they differ in rounding.
 
-params: hidden_size, heads, dim, rot_dim, vdim, q_rank, kv_rank, scale, eps, rot_dims (default rot_dim), rot_base, and the
-tensor names dq, dq_norm, uq, dkv, dkv_norm, uk, uv, g, o (`<key>_name`).
+Three things are optional. Without a query latent (`q_rank` None) the queries are one product, q = Wq h, laid out head
+by head as [plain | rotated]. Without `gate` the heads go to Wo as they are. With `window` a row at position i sees the
+keys j with 0 <= i - j < window; the cache is then of the kind "window" (pages that no later query sees go back to the
+pool while the request runs), and a portion's keys and values are made from the first kept page on.
+
+params: hidden_size, heads, dim, rot_dim, vdim, q_rank (None: no query latent), kv_rank, scale, eps, rot_dims (default
+rot_dim), rot_base, gate (default True), window (default None), and the tensor names dq, dq_norm, uq (or q), dkv, dkv_norm,
+uk, uv, g, o (`<key>_name`).
 """
 from __future__ import annotations
 
@@ -32,8 +38,8 @@ from ..weights import ParamSpec
 from . import planes
 from .registry import CacheNeed, Mixer, register_part, to_compute
 
-_DEFAULT_NAMES = dict(dq="mix.dq", dq_norm="mix.dq.norm", uq="mix.uq", dkv="mix.dkv", dkv_norm="mix.dkv.norm", uk="mix.uk",
-                      uv="mix.uv", g="mix.g", o="mix.o")
+_DEFAULT_NAMES = dict(dq="mix.dq", dq_norm="mix.dq.norm", uq="mix.uq", q="mix.q", dkv="mix.dkv", dkv_norm="mix.dkv.norm",
+                      uk="mix.uk", uv="mix.uv", g="mix.g", o="mix.o")
 
 
 class LatentAttentionMixer(Mixer):
@@ -42,34 +48,42 @@ class LatentAttentionMixer(Mixer):
         p = params
         self.hidden, self.heads = int(p["hidden_size"]), int(p["heads"])
         self.dim, self.rot_dim, self.vdim = int(p["dim"]), int(p["rot_dim"]), int(p["vdim"])
-        self.q_rank, self.kv_rank = int(p["q_rank"]), int(p["kv_rank"])
+        self.q_rank, self.kv_rank = int(p["q_rank"]) if p.get("q_rank") else 0, int(p["kv_rank"])
+        self.gated, self.window = bool(p.get("gate", True)), int(p["window"]) if p.get("window") else 0
         self.scale, self.eps = float(p["scale"]), float(p["eps"])
         self.rot_dims, self.rot_base = int(p.get("rot_dims", self.rot_dim)), float(p.get("rot_base", 10000.0))
         if self.rot_dims % 2 or self.rot_dims > self.rot_dim:
             raise ValueError(f"latent attention: {self.rot_dims} rotated dimensions of a rotated part of {self.rot_dim}")
-        self.names = {k: prefix + p.get(k + "_name", d) for k, d in _DEFAULT_NAMES.items()}
+        unused = (("q",) if self.q_rank else ("dq", "dq_norm", "uq")) + (() if self.gated else ("g",))
+        self.names = {k: prefix + p.get(k + "_name", d) for k, d in _DEFAULT_NAMES.items() if k not in unused}
         self.w_in = self.w_uq = self.wo = self.wuk_t = self.wuv_t = self.table = None
         if not ctx.is_meta:
             self.table = ops.shared_rope_table(self.rot_dims, self.rot_base, ctx.max_model_len, ctx.device)
 
     def param_specs(self):
         n, W, H = self.names, self.hidden, self.heads
-        return [ParamSpec(n["dq"], (self.q_rank, W)), ParamSpec(n["dq_norm"], (self.q_rank,), init="ones"),
-                ParamSpec(n["uq"], (H * (self.dim + self.rot_dim), self.q_rank)),
-                ParamSpec(n["dkv"], (self.kv_rank + self.rot_dim, W)), ParamSpec(n["dkv_norm"], (self.kv_rank,), init="ones"),
-                ParamSpec(n["uk"], (H * self.dim, self.kv_rank)), ParamSpec(n["uv"], (H * self.vdim, self.kv_rank)),
-                ParamSpec(n["g"], (H * self.vdim, W)), ParamSpec(n["o"], (W, H * self.vdim))]
+        if self.q_rank:
+            specs = [ParamSpec(n["dq"], (self.q_rank, W)), ParamSpec(n["dq_norm"], (self.q_rank,), init="ones"),
+                     ParamSpec(n["uq"], (H * (self.dim + self.rot_dim), self.q_rank))]
+        else:
+            specs = [ParamSpec(n["q"], (H * (self.dim + self.rot_dim), W))]
+        specs += [ParamSpec(n["dkv"], (self.kv_rank + self.rot_dim, W)), ParamSpec(n["dkv_norm"], (self.kv_rank,), init="ones"),
+                  ParamSpec(n["uk"], (H * self.dim, self.kv_rank)), ParamSpec(n["uv"], (H * self.vdim, self.kv_rank))]
+        if self.gated:
+            specs.append(ParamSpec(n["g"], (H * self.vdim, W)))
+        return specs + [ParamSpec(n["o"], (W, H * self.vdim))]
 
     def load(self, tensors):
         t = {k: to_compute(tensors[n], self.ctx) for k, n in self.names.items()}
-        mats = [t["dq"], t["dkv"], t["g"]]
+        mats = [t["dq"] if self.q_rank else t["q"], t["dkv"]] + ([t["g"]] if self.gated else [])
         dt = mats[0].dtype if all(m.dtype == mats[0].dtype for m in mats) else torch.float32
-        self.w_in = ops.Weight(torch.cat([m.to(dt) for m in mats], 0).contiguous())      # rows [dq | dkv | g]
-        self.w_uq, self.wo = ops.Weight(t["uq"]), ops.Weight(t["o"])
+        self.w_in = ops.Weight(torch.cat([m.to(dt) for m in mats], 0).contiguous())      # rows [dq or q | dkv | g]
+        self.w_uq, self.wo = ops.Weight(t["uq"]) if self.q_rank else None, ops.Weight(t["o"])
         H = self.heads
         self.wuk_t = t["uk"].reshape(H, self.dim, self.kv_rank).contiguous()                      # [h][d][r]
         self.wuv_t = t["uv"].reshape(H, self.vdim, self.kv_rank).transpose(1, 2).contiguous()     # [h][r][e]
-        self.wq_norm, self.wc_norm = t["dq_norm"], t["dkv_norm"].to(t["dq_norm"].dtype)
+        self.wc_norm = t["dkv_norm"]
+        self.wq_norm = t["dq_norm"].to(self.wc_norm.dtype) if self.q_rank else None
         # for portions: [keys of every head | values of every head] = [c | kr] @ w_kv^T in one product
         self.w_kv = None
         D, Dr, E, R = self.dim, self.rot_dim, self.vdim, self.kv_rank
@@ -83,41 +97,53 @@ class LatentAttentionMixer(Mixer):
             self.w_kv = ops.Weight(torch.cat([wk.reshape(H * (D + Dr), R + Dr), wv], 0).contiguous())
 
     def weight_bytes(self):
-        return (self.w_in.nbytes + self.w_uq.nbytes + self.wo.nbytes
+        return (self.w_in.nbytes + (self.w_uq.nbytes if self.w_uq is not None else 0) + self.wo.nbytes
                 + sum(w.numel() * w.element_size() for w in (self.wuk_t, self.wuv_t)))
 
     def cache_need(self):
         width = self.kv_rank + self.rot_dim
+        if self.window:
+            return CacheNeed("window", 1, width, self.window, (("ckr", 1, width),))
         return CacheNeed("full", 1, width, 0, (("ckr", 1, width),))
 
     def forward(self, xn, x, batch, cache, state):
         T, H, dev = xn.shape[0], self.heads, xn.device
         Rq, R, Dr, D, E = self.q_rank, self.kv_rank, self.rot_dim, self.dim, self.vdim
-        proj = torch.empty(T, Rq + R + Dr + H * E, dtype=torch.float32, device=dev)
+        Q0 = Rq if Rq else H * (D + Dr)          # the first columns of the product: the raw query latent, or the queries
+        proj = torch.empty(T, Q0 + R + Dr + (H * E if self.gated else 0), dtype=torch.float32, device=dev)
         ops.linear_rows32(xn, self.w_in, proj)
         ckr = cache.planes["ckr"]
         cq = torch.empty(T, Rq, dtype=self.ctx.dtype, device=dev)
-        ops.latent_prepare(proj, (0, Rq, Rq + R), self.wq_norm, self.wc_norm, batch.positions,
+        ops.latent_prepare(proj, (0, Q0, Q0 + R), self.wq_norm, self.wc_norm, batch.positions,
                            batch.slot_maps[cache.group] if cache.write else None, self.table, self.rot_dims, self.eps, cq, ckr,
                            Rq, R, Dr, self.ctx.page_size)
-        q = torch.empty(T, H * (D + Dr), dtype=torch.float32, device=dev)
-        ops.linear_rows32(cq, self.w_uq, q)
+        if Rq:
+            q = torch.empty(T, H * (D + Dr), dtype=torch.float32, device=dev)
+            ops.linear_rows32(cq, self.w_uq, q)
+        else:
+            q = proj[:, :Q0]
+        gate = dict(gate=proj, gate_offset=Q0 + R + Dr) if self.gated else {}
+        mask = dict(mask="window", window=self.window) if self.window else dict(mask="causal")
         att = torch.empty(T, H * E, dtype=self.ctx.dtype, device=dev)
-        # requests that bring many rows: keys and values of their whole context from one product, tensor-core attention
+        # requests that bring many rows: keys and values of what they can see from one product, tensor-core attention
         many = [r for r in range(batch.n_requests) if batch.h_q_len[r] >= ops.MASKED_FLASH_MIN_ROWS] \
             if self.w_kv is not None and ops.fast_kernels_on() else []
         if many:
             qb = torch.empty(T, H * (D + Dr), dtype=self.ctx.dtype, device=dev)
             ops.rope_norm_store(q, (0, 0, 0), batch.positions, None, self.table, self.rot_dims, "interleaved", False, 0.0, qb,
                                 None, None, H, 1, D + Dr, E, self.ctx.page_size, rot_off=D)
+            ps = self.ctx.page_size
             for r in many:
-                n = batch.h_ctx_len[r] + batch.h_q_len[r]
+                ctx_len = batch.h_ctx_len[r]
+                # with a window: from the page of the first key that the portion's first row sees
+                first = (max(0, ctx_len - self.window + 1) // ps) * ps if self.window else 0
+                n = ctx_len + batch.h_q_len[r] - first
                 rows = torch.empty(n, R + Dr, dtype=self.ctx.dtype, device=dev)
-                ops.gather_rows(ckr, batch.block_tables[cache.group][r], rows, n, self.ctx.page_size)
+                ops.gather_rows(ckr, batch.block_tables[cache.group][r][first // ps:], rows, n, ps)
                 kv = torch.empty(n, H * (D + Dr + E), dtype=self.ctx.dtype, device=dev)
                 ops.linear(rows, self.w_kv, kv)
                 ops.attention_flash_tokens(qb, kv[:, :H * (D + Dr)], kv[:, H * (D + Dr):], batch, r, att, H, H, D + Dr, E,
-                                           self.scale, gate=proj, gate_offset=Rq + R + Dr)
+                                           self.scale, window=self.window, first_pos=first, **gate)
             planes.record(batch, "q", qb)
             if len(many) == batch.n_requests:
                 planes.record(batch, "attention", att)
@@ -128,9 +154,9 @@ class LatentAttentionMixer(Mixer):
         ops.heads_linear(q, D + Dr, self.wuk_t, qa, R + Dr, tail=Dr, rot=self.rot_dims, positions=batch.positions,
                          table=self.table, batch=batch, row_limit=limit)
         lat = torch.empty(T, H * R, dtype=torch.float32, device=dev)               # per head the softmax-weighted sum of c
-        ops.attention_masked(qa, ckr, ckr, batch, cache.group, lat, H, 1, R + Dr, R, self.ctx.page_size, self.scale, "causal",
-                             row_limit=limit)
-        ops.heads_linear(lat, R, self.wuv_t, att, E, gate=proj, gate_offset=Rq + R + Dr, batch=batch, row_limit=limit)
+        ops.attention_masked(qa, ckr, ckr, batch, cache.group, lat, H, 1, R + Dr, R, self.ctx.page_size, self.scale,
+                             row_limit=limit, **mask)
+        ops.heads_linear(lat, R, self.wuv_t, att, E, batch=batch, row_limit=limit, **gate)
         if not many:
             planes.record(batch, "q", qa)
         planes.record(batch, "attention", att)

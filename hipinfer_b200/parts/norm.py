@@ -86,5 +86,39 @@ class LayerNorm(Part):
         return ops.layernorm(x, self.weight, self.eps, out, rows, self.bias)
 
 
+class StreamsRMSNorm(Part):
+    """RMSNorm of a weighted sum of residual streams: u = sum_s read[s] x_s, y = w * u / sqrt(mean(u^2) + eps), for rows
+    x float32 [T, streams * size]; all 32-bit, rounded once. The read weights are a tensor [streams] (`read_name`); without
+    one the streams are summed as they are (the norm before the head). params: name, size, eps, streams, read_name."""
+
+    def __init__(self, params, ctx, prefix=""):
+        super().__init__(params, ctx, prefix)
+        self.size, self.eps, self.streams = int(params["size"]), float(params["eps"]), int(params["streams"])
+        self.name = prefix + params["name"]
+        self.read_name = prefix + params["read_name"] if params.get("read_name") else None
+        self.weight = self.read = None
+
+    def param_specs(self):
+        specs = [ParamSpec(self.name, (self.size,), init="ones")]
+        if self.read_name:
+            specs.append(ParamSpec(self.read_name, (self.streams,), init="ones"))
+        return specs
+
+    def load(self, tensors):
+        self.weight = to_compute(tensors[self.name], self.ctx)
+        if self.read_name:
+            self.read = tensors[self.read_name].to(torch.float32).contiguous()
+
+    def weight_bytes(self):
+        return self.weight.numel() * self.weight.element_size()
+
+    def forward(self, x, rows=None, out=None):
+        M = x.shape[0] if rows is None else rows.numel()
+        if out is None:
+            out = torch.empty(M, self.size, dtype=self.ctx.dtype, device=x.device)
+        return ops.streams_norm(x, self.read, self.weight, self.eps, out, self.streams, rows)
+
+
 register_part("norm", "rmsnorm", RMSNorm)
 register_part("norm", "layernorm", LayerNorm)
+register_part("norm", "streams_rmsnorm", StreamsRMSNorm)
