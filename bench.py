@@ -492,7 +492,34 @@ def vegodra_configs(size: dict, window: int):
     return vegodra, llama
 
 
-DESIGNS = {"torirax": design_configs, "vegodra": vegodra_configs}
+def runopel_configs(size: dict, window: int):
+    """(Runopel config, Vegodra config) of equal width, depth, head counts and feed-forward width; Vegodra is the closest
+    of the other designs (latent attention and a linear recurrence with a state matrix per head). Runopel's layers stand
+    where Vegodra's like layers stand: latent attention (here with a sliding window of `window` positions and no query
+    latent) at 0 and 2 of every four, the state-space mixer (heads x head_dim value channels, 128 state channels in
+    kv-heads groups, four taps) at 1 and 3. Feed-forwards alternate between the dense one with limits and eight experts
+    of half the dense width, two per token (as many active weights as the dense one). Two residual streams."""
+    W, L, H, G, D = size["width"], size["layers"], size["heads"], size["kv"], size["head_dim"]
+    layers = []
+    for i in range(L):
+        if i % 2 == 0:
+            mlp = dict(kind="dense", ff=size["ff"], limit=7.0)
+        else:
+            mlp = dict(kind="moe", expert=dict(ff=size["ff"] // 2), router=dict(experts=8, top=2))
+        if i % 4 in (0, 2):
+            m = dict(heads=H, dim=D, rot_dim=D // 2, vdim=D, kv_rank=4 * D, scale=(D + D // 2) ** -0.5,
+                     rot=dict(base=10000.0, dims=D // 2), mask=dict(size=window))
+            layers.append(dict(type="latent_attention", mixer=m, mlp=mlp))
+        else:
+            m = dict(heads=H, vdim=D, state=128, groups=G, norm_groups=G, conv=4)
+            layers.append(dict(type="mamba2", mixer=m, mlp=mlp))
+    runopel = dict(architecture="Runopel", vocab=size["vocab"], width=W, max_positions=CONTEXT_LEN, norm=dict(eps=1e-5),
+                   residual_mult=0.5, logit_scale=0.5, streams=2, layers=layers)
+    return runopel, vegodra_configs(size, window)[0]
+
+
+DESIGNS = {"torirax": design_configs, "vegodra": vegodra_configs, "runopel": runopel_configs}
+BESIDE = {"torirax": "llama", "vegodra": "llama", "runopel": "vegodra"}
 
 
 def kernel_table(one, reps: int = 3):
@@ -536,8 +563,9 @@ def kernel_table(one, reps: int = 3):
 
 
 def design_bench(a) -> int:
-    """Prefill and decode throughput of the chosen design (Torirax or Vegodra) and of the Llama decoder at equal layer
-    sizes, with each step's kernels by name; one JSON line. The default run of this file is untouched by this option."""
+    """Prefill and decode throughput of the chosen design and of the model beside it (the Llama decoder for Torirax and
+    Vegodra, Vegodra for Runopel) at equal layer sizes, with each step's kernels by name; one JSON line. The default run
+    of this file is untouched by this option."""
     import torch
 
     from hipinfer_b200 import Engine
@@ -546,7 +574,7 @@ def design_bench(a) -> int:
 
     global PROMPT_LEN, PREFILL_TOKENS
     PROMPT_LEN, PREFILL_TOKENS = a.prompt, a.prefill_tokens
-    out = {"design": a.design, "beside": "llama", "dtype": "bf16", "data": "synthetic: random token ids, random weights",
+    out = {"design": a.design, "beside": BESIDE[a.design], "dtype": "bf16", "data": "synthetic: random token ids, random weights",
            "prompt": PROMPT_LEN, "prefill_tokens": PREFILL_TOKENS, "window": a.window, "sizes": {}}
     clocks = ClockSampler().start()
     batches = [1, 8, 64]
@@ -557,7 +585,7 @@ def design_bench(a) -> int:
             size["layers"] = a.layers
         MODEL["vocab_size"] = size["vocab"]
         res = {}
-        for which, cfg in zip((a.design, "llama"), DESIGNS[a.design](size, a.window)):
+        for which, cfg in zip((a.design, BESIDE[a.design]), DESIGNS[a.design](size, a.window)):
             pages_per_seq = -(-(PROMPT_LEN + a.steps + a.warmup + 16 + 4 * PAGE) // PAGE)
             eng = Engine(config=cfg, random_weights=0, std=0.02, dtype="bfloat16", max_batch=max(batches), max_seq=CONTEXT_LEN,
                          max_prefill=max(PREFILL_TOKENS, PROMPT_LEN), page_size=PAGE,
@@ -681,10 +709,10 @@ def main() -> int:
     ap.add_argument("--breakdown", action="store_true", help="print per-kernel times of a decode step and exit")
     ap.add_argument("--prefill", action="store_true", help="with --breakdown: the prefill step instead of a decode step")
     ap.add_argument("--design", default=None, choices=sorted(DESIGNS),
-                    help="prefill and decode of this design beside the Llama decoder at equal layer sizes (see --sizes); "
+                    help="prefill and decode of this design beside its closest other model at equal layer sizes (see --sizes); "
                          "the default run is not changed by it")
     ap.add_argument("--sizes", default="1b", help="with --design: layer sizes, of " + ", ".join(sorted(DESIGN_SIZES)) + " (commas between)")
-    ap.add_argument("--window", type=int, default=1024, help="with --design: the attention window (torirax: the first 4 tokens are kept) or chunk size (vegodra)")
+    ap.add_argument("--window", type=int, default=1024, help="with --design: the attention window (torirax: the first 4 tokens are kept; runopel) or chunk size (vegodra)")
     a = ap.parse_args()
     if a.impl == "reference":
         return reference_arm(a)

@@ -159,9 +159,12 @@ def sub(tensors, prefix):
     return {k[len(prefix):]: v.to(F) for k, v in tensors.items() if k.startswith(prefix)}
 
 
-def forward(cfg, tensors, tokens, layers_out=None):
+def forward(cfg, tensors, tokens, layers_out=None, round_to=None):
     """Logits [T, vocab] of one sequence from position 0. cfg: the config.json dictionary; tensors: name -> tensor.
-    layers_out (a list): the residual stream (the sum of the streams) after every layer is appended."""
+    layers_out (a list): the residual stream (the sum of the streams) after every layer is appended.
+    round_to (a dtype): every sublayer's input and result are rounded to it; the difference to the exact logits measures
+    how sensitive each position is to rounding."""
+    rd = (lambda t: t) if round_to is None else (lambda t: t.to(round_to).to(F))
     eps = cfg["norm"]["eps"]
     m = float(cfg.get("residual_mult", 1.0))
     S = cfg.get("streams")
@@ -189,10 +192,10 @@ def forward(cfg, tensors, tokens, layers_out=None):
             if S:
                 c = sub(t, hc)
                 u = sum(c["in"][s] * xs[s] for s in range(S))
-                y = fn(rms_div(u, eps) * t[norm])
+                y = rd(fn(rd(rms_div(u, eps) * t[norm])))
                 xs = [sum(c["mix"][s, k] * xs[s] for s in range(S)) + m * c["out"][k] * y for k in range(S)]
             else:
-                xs = [xs[0] + m * fn(rms_div(xs[0], eps) * t[norm])]
+                xs = [xs[0] + m * rd(fn(rd(rms_div(xs[0], eps) * t[norm])))]
         if layers_out is not None:
             layers_out.append(sum(xs))
     x = sum(xs)
