@@ -8,8 +8,11 @@
 //                             S <- a S + (dt B_g) x_h^T;  y = S^T C_g + D_h x_h
 //   ssd_gate_norm_kernel  y <- y silu(z), then the row in `parts` equal parts, each divided by its own root mean square
 //                         (eps inside the root) and multiplied by a weight; rounded once
+//   Long portions run the recurrence in three launches instead, over pieces of L tokens: every piece from a zero state
+//   (its own contribution and the product of its decays), then the pieces' starting states one after another
+//   (ssd_carry_kernel), then every piece again from its starting state for y. The walk is the same code in all three.
 // Everything here is 32-bit. Requests, lengths and state slots come from device arrays, so a decode step can be replayed
-// from a CUDA graph; a token's arithmetic does not depend on where a portion or a chunk starts.
+// from a CUDA graph; where a portion or a piece starts changes a token's result by rounding only.
 #include "common.cuh"
 
 constexpr int SC_TAPS_MAX = 8;     // most convolution taps
@@ -115,7 +118,14 @@ struct SsdArgs {
   const int* q_start; const int* q_len; const int* slot;
   float* y;                              // [T][H P]
   int H, P, N, G, KS, vec4;
+  float* piece_state;                    // pieces only: [requests][pieces][H][N][P]
+  float* piece_decay;                    // pieces only: [requests][pieces][H]
+  int L, pieces;                         // tokens a piece, most pieces a request
 };
+
+// MODE of the walk: whole portions from and into the state slot; a piece from zero (no y; leaves its state and the product
+// of its decays); a piece from its starting state (y only).
+enum { SS_WHOLE = 0, SS_PIECE_LOCAL = 1, SS_PIECE_OUT = 2 };
 
 __device__ __forceinline__ void ss_cp16(float* dst, const float* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
@@ -126,7 +136,7 @@ __device__ __forceinline__ void ss_cp4(float* dst, const float* src) {
 
 template <int DPT> struct SsdThreads { static constexpr int MAX = DPT <= 8 ? 1024 : DPT <= 32 ? 512 : 256; };
 
-template <int DPT, typename TW>
+template <int DPT, typename TW, int MODE>
 __global__ void __launch_bounds__(SsdThreads<DPT>::MAX, 1) ssd_scan_kernel(SsdArgs A) {
   extern __shared__ __align__(16) float ssm[];
   hb_pdl_launch();
@@ -136,16 +146,21 @@ __global__ void __launch_bounds__(SsdThreads<DPT>::MAX, 1) ssd_scan_kernel(SsdAr
   const int g = h / (H / A.G);
   const int p = tid / KS, ks = tid - p * KS;
   const bool live = p < P;
-  const int t0 = A.q_start[r], len = A.q_len[r];
-  float* S_g = A.state + ((size_t)A.slot[r] * H + h) * N * P;
+  const int t0 = A.q_start[r];
+  const int j_begin = MODE == SS_WHOLE ? 0 : (int)blockIdx.z * A.L;
+  const int len = MODE == SS_WHOLE ? A.q_len[r] : min(A.q_len[r], j_begin + A.L);      // the walk ends here
+  if (MODE != SS_WHOLE && j_begin >= len) return;
+  float* S_g = MODE == SS_WHOLE ? A.state + ((size_t)A.slot[r] * H + h) * N * P
+                                : A.piece_state + (((size_t)r * A.pieces + blockIdx.z) * H + h) * N * P;
   // a token's row in shared memory: [B -> dt B (N) | C (N) | x (P) | dt_raw -> decay (1) | pad], two chunks deep
   const int RW = ((2 * N + P + 1 + 3) / 4) * 4;
   float S[DPT];
 #pragma unroll
   for (int i = 0; i < DPT; i++) {
     const int n = i * KS + ks;
-    S[i] = (live && n < N) ? S_g[(size_t)n * P + p] : 0.f;
+    S[i] = (MODE != SS_PIECE_LOCAL && live && n < N) ? S_g[(size_t)n * P + p] : 0.f;
   }
+  float decays = 1.f;
   const float dtb = hb_to_float(((const TW*)A.dt_bias)[h]);
   const float neg_a = -expf(hb_to_float(((const TW*)A.a_log)[h]));
   const float dsk = hb_to_float(((const TW*)A.d_skip)[h]);
@@ -174,9 +189,9 @@ __global__ void __launch_bounds__(SsdThreads<DPT>::MAX, 1) ssd_scan_kernel(SsdAr
     for (int j = tid; j < n; j += nthr) ss_cp4(st + j * RW + 2 * N + P, A.dt + (size_t)(t0 + c0 + j) * A.lddt + h);
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
-  if (len > 0) fetch(0, 0);
+  if (len > j_begin) fetch(0, j_begin);
   int buf = 0;
-  for (int c0 = 0; c0 < len; c0 += SS_CH, buf ^= 1) {
+  for (int c0 = j_begin; c0 < len; c0 += SS_CH, buf ^= 1) {
     const int n = min(SS_CH, len - c0);
     if (c0 + SS_CH < len) {
       fetch(buf ^ 1, c0 + SS_CH);
@@ -208,6 +223,15 @@ __global__ void __launch_bounds__(SsdThreads<DPT>::MAX, 1) ssd_scan_kernel(SsdAr
       const float a = row[2 * N + P];
       const float* Bj = row;
       const float* Cj = row + N;
+      if (MODE == SS_PIECE_LOCAL) {
+        decays *= a;
+#pragma unroll
+        for (int i = 0; i < DPT; i++) {
+          const int n0 = i * KS + ks;
+          if (n0 < N) S[i] = fmaf(a, S[i], Bj[n0] * xv);
+        }
+        continue;
+      }
       float o = 0.f, o2 = 0.f;
 #pragma unroll
       for (int i = 0; i < DPT; i += 2) {
@@ -227,17 +251,45 @@ __global__ void __launch_bounds__(SsdThreads<DPT>::MAX, 1) ssd_scan_kernel(SsdAr
     }
     __syncthreads();             // the buffer is free for the chunk after the next
   }
+  if (MODE == SS_PIECE_OUT) return;
 #pragma unroll
   for (int i = 0; i < DPT; i++) {
     const int n = i * KS + ks;
     if (live && n < N) S_g[(size_t)n * P + p] = S[i];
   }
+  if (MODE == SS_PIECE_LOCAL && tid == 0) A.piece_decay[((size_t)r * A.pieces + blockIdx.z) * H + h] = decays;
+}
+
+// The pieces' starting states, one after another: an element of (request, head) walks its pieces, leaves in each the state
+// the piece starts from and carries (decay product) * state + the piece's own contribution on; the last goes to the slot.
+__global__ void __launch_bounds__(256) ssd_carry_kernel(SsdArgs A) {
+  hb_pdl_launch();
+  hb_pdl_wait();
+  const int r = blockIdx.y, NP = A.N * A.P;
+  const size_t e = (size_t)blockIdx.x * 256 + threadIdx.x;
+  if (e >= (size_t)A.H * NP) return;
+  const int h = (int)(e / NP), len = A.q_len[r];
+  if (len <= 0) return;
+  const int pieces = (len + A.L - 1) / A.L;
+  float* slot = A.state + (size_t)A.slot[r] * A.H * NP + e;
+  float carry = *slot;
+  for (int c = 0; c < pieces; c++) {
+    float* ps = A.piece_state + ((size_t)r * A.pieces + c) * A.H * NP + e;
+    const float own = *ps;
+    *ps = carry;
+    carry = fmaf(A.piece_decay[((size_t)r * A.pieces + c) * A.H + h], carry, own);
+  }
+  *slot = carry;
 }
 
 HB_EXPORT int hb_ssd_scan(const float* xbc, long ldx, const float* dt, long lddt, const void* dt_bias, const void* a_log,
                           const void* d_skip, int w_dt, float* state, const int* q_start, const int* q_len, const int* slot,
-                          float* y, int n_requests, int H, int P, int N, int G, cudaStream_t s) {
+                          float* y, int n_requests, int H, int P, int N, int G, int piece_len, int pieces, float* piece_state,
+                          float* piece_decay, cudaStream_t s) {
+  // pieces > 0: the three-launch form over pieces of piece_len tokens, with room for `pieces` pieces a request in
+  // piece_state [n_requests][pieces][H][N][P] and piece_decay [n_requests][pieces][H]
   if (n_requests <= 0) return 0;
+  if (pieces > 0 && (piece_len <= 0 || !piece_state || !piece_decay || pieces > 65535)) HB_FAIL("hb_ssd_scan: %d pieces of %d", pieces, piece_len);
   if (P > 1024 || G <= 0 || H % G) HB_FAIL("hb_ssd_scan: %d heads of %d in %d groups", H, P, G);
   // threads a value channel (a power of two up to 32): the fewest that give the block 256 threads, else the most that fit
   int ks = 0;
@@ -255,22 +307,38 @@ HB_EXPORT int hb_ssd_scan(const float* xbc, long ldx, const float* dt, long lddt
   A.xbc = xbc; A.ldx = ldx; A.dt = dt; A.lddt = lddt; A.dt_bias = dt_bias; A.a_log = a_log; A.d_skip = d_skip; A.state = state;
   A.q_start = q_start; A.q_len = q_len; A.slot = slot; A.y = y; A.H = H; A.P = P; A.N = N; A.G = G; A.KS = ks;
   A.vec4 = !((N | P) & 3) && !(ldx & 3) && !((uintptr_t)xbc & 15);
+  A.piece_state = piece_state; A.piece_decay = piece_decay; A.L = piece_len; A.pieces = pieces;
   const int threads = ((P * ks + 31) / 32) * 32;
   const int RW = ((2 * N + P + 1 + 3) / 4) * 4;
   const size_t smem = (size_t)2 * SS_CH * RW * sizeof(float);
   if (smem > 200 * 1024) HB_FAIL("hb_ssd_scan: heads of %d x %d do not fit shared memory", N, P);
-  dim3 grid(H, n_requests);
-#define SS_LAUNCH(DPT)                                                                                             \
+  if (n_requests > 65535) HB_FAIL("hb_ssd_scan: the grid is too large");
+#define SS_LAUNCH_MODE(DPT, MODE, GRID)                                                                            \
   HB_DISPATCH_1(w_dt, "hb_ssd_scan", do {                                                                          \
-    auto kern = ssd_scan_kernel<DPT, TA>;                                                                          \
+    auto kern = ssd_scan_kernel<DPT, TA, MODE>;                                                                    \
     if (smem + 4096 > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
-    hb_launch(kern, grid, dim3(threads), smem, s, A);                                                              \
+    hb_launch(kern, GRID, dim3(threads), smem, s, A);                                                              \
   } while (0))
-  if (per <= 8) SS_LAUNCH(8);
-  else if (per <= 16) SS_LAUNCH(16);
-  else if (per <= 32) SS_LAUNCH(32);
-  else SS_LAUNCH(64);
+#define SS_LAUNCH(MODE, GRID)                                                                                      \
+  do {                                                                                                             \
+    if (per <= 8) SS_LAUNCH_MODE(8, MODE, GRID);                                                                   \
+    else if (per <= 16) SS_LAUNCH_MODE(16, MODE, GRID);                                                            \
+    else if (per <= 32) SS_LAUNCH_MODE(32, MODE, GRID);                                                            \
+    else SS_LAUNCH_MODE(64, MODE, GRID);                                                                           \
+  } while (0)
+  if (pieces <= 0) {
+    SS_LAUNCH(SS_WHOLE, dim3(H, n_requests));
+  } else {
+    const dim3 grid(H, n_requests, pieces);
+    SS_LAUNCH(SS_PIECE_LOCAL, grid);
+    HB_CHECK_LAUNCH("hb_ssd_scan");
+    const size_t elems = (size_t)H * N * P;
+    hb_launch(ssd_carry_kernel, dim3((unsigned)((elems + 255) / 256), n_requests), dim3(256), 0, s, A);
+    HB_CHECK_LAUNCH("hb_ssd_scan");
+    SS_LAUNCH(SS_PIECE_OUT, grid);
+  }
 #undef SS_LAUNCH
+#undef SS_LAUNCH_MODE
   HB_CHECK_LAUNCH("hb_ssd_scan");
   return 0;
 }

@@ -64,7 +64,7 @@ _SIGS = {
         "hb_glu_bias": [_p, _l, _p, _i, _p, _i, _l, _i, _i, _i, _i, _f, _f, _p],
         "hb_scale_bias_rows": [_p, _l, _p, _i, _f, _i, _i, _p],
         "hb_ssd_conv": [_p, _l, _i, _p, _p, _i, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p],
-        "hb_ssd_scan": [_p, _l, _p, _l, _p, _p, _p, _i, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p],
+        "hb_ssd_scan": [_p, _l, _p, _l, _p, _p, _p, _i, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _p, _p],
         "hb_ssd_gate_norm": [_p, _p, _l, _p, _i, _p, _i, _i, _i, _i, _f, _p],
         "hb_moe_route": [_p, _i, _l, _p, _i, _p, _p, _i, _i, _i, _i, _p],
         "hb_moe_gate_up_rows": [_p, _i, _l, _p, _i, _p, _p, _p, _i, _i, _i, _i, _p],
@@ -1098,12 +1098,19 @@ def ssd_conv(proj: torch.Tensor, offset: int, weight: torch.Tensor, bias: torch.
     return out
 
 
+SSD_PIECE_TOKENS = 64    # tokens a piece of the state-space recurrence (ssd_scan); 0: always one walk a request
+
+
 def ssd_scan(xbc: torch.Tensor, dt: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor, d_skip: torch.Tensor,
              state: torch.Tensor, batch, y: torch.Tensor, heads: int, vdim: int, n_state: int, groups: int) -> torch.Tensor:
     """The state-space recurrence with a scalar decay per head over the step's rows, request by request, from and into
     each request's state slot (csrc/ssd.cu). xbc float32 [T, heads * vdim | groups * n_state | groups * n_state] (x, B, C
     after the convolution), dt float32 [T, heads] raw (a view of wider rows is fine), state float32
-    [slots, heads, n_state, vdim], y float32 [T, heads * vdim]."""
+    [slots, heads, n_state, vdim], y float32 [T, heads * vdim].
+
+    A step whose longest portion has at least three times SSD_PIECE_TOKENS rows runs in pieces of that many tokens (every
+    piece from a zero state, the pieces' starting states one after another, every piece again for y), so that a long
+    prompt fills the GPU instead of one block a head; the results differ from the walk in one go by rounding only."""
     _need_cuda(xbc, dt, dt_bias, a_log, d_skip, state, y)
     _rows_contiguous(xbc, "ssd_scan xbc")
     _rows_contiguous(dt, "ssd_scan dt")
@@ -1112,10 +1119,15 @@ def ssd_scan(xbc: torch.Tensor, dt: torch.Tensor, dt_bias: torch.Tensor, a_log: 
     assert xbc.shape[1] == heads * vdim + 2 * groups * n_state and dt.shape == (T, heads) and y.shape == (T, heads * vdim)
     assert state.shape[1:] == (heads, n_state, vdim) and dt_bias.dtype == a_log.dtype == d_skip.dtype
     assert dt_bias.numel() == a_log.numel() == d_skip.numel() == heads
+    L, pieces, piece_state, piece_decay = int(SSD_PIECE_TOKENS), 0, None, None
+    if L > 0 and batch.max_q_len >= 3 * L:
+        pieces = -(-batch.max_q_len // L)
+        piece_state = torch.empty(batch.n_requests, pieces, heads, n_state, vdim, dtype=torch.float32, device=xbc.device)
+        piece_decay = torch.empty(batch.n_requests, pieces, heads, dtype=torch.float32, device=xbc.device)
     _call("hybrid", "hb_ssd_scan", xbc.data_ptr(), xbc.stride(0), dt.data_ptr(), dt.stride(0), dt_bias.data_ptr(),
           a_log.data_ptr(), d_skip.data_ptr(), _dt(dt_bias), state.data_ptr(), batch.req_q_start.data_ptr(),
           batch.req_q_len.data_ptr(), batch.req_state_slot.data_ptr(), y.data_ptr(), batch.n_requests, heads, vdim, n_state,
-          groups, _stream())
+          groups, L, pieces, piece_state.data_ptr() if pieces else None, piece_decay.data_ptr() if pieces else None, _stream())
     return y
 
 

@@ -18,14 +18,17 @@ TOL = {"float32": 3e-5, "bfloat16": 2.5e-2}
 
 def _close(got, ref, dtype, what, sens=None):
     """32-bit: every position within the bound. bfloat16: a position's bound is the general one or, where that is larger,
-    six times the position's own sensitivity to rounding (tests/runopel_models.py: a norm that divides by nearly nothing,
-    sums that cancel); up to 3 % of a request's positions (at least one) may lie over their bound, none over four times."""
+    six times the sensitivity to rounding of the position and its two neighbours on either side (tests/runopel_models.py: a
+    norm that divides by nearly nothing, sums that cancel; the estimate is one draw of rounding noise, and what makes a
+    position sensitive also holds a token earlier or later through the recurrent state); up to 3 % of a request's positions
+    (at least one) may lie over their bound, none over four times."""
     scale = float(ref.abs().max())
     assert got.shape == ref.shape and torch.isfinite(got).all(), what
     bad = (got.double() - ref.double()).abs().amax(-1) / scale
     bound = torch.full_like(bad, TOL[dtype])
     if dtype == "bfloat16" and sens is not None:
-        bound = torch.maximum(bound, 6.0 * sens[:bad.shape[0]].double())
+        near = torch.nn.functional.max_pool1d(sens[:bad.shape[0]].double()[None, None], 5, 1, 2)[0, 0]
+        bound = torch.maximum(bound, 6.0 * near)
     over = int((bad > bound).sum())
     allowed = 0 if dtype == "float32" else max(1, (3 * got.shape[0]) // 100)
     if over > allowed or bool((bad > 4 * bound).any()):
@@ -70,6 +73,17 @@ def _check(setup, plan, what):
 
 def test_whole_prompts(setup):
     _check(setup, tiny.plan_whole(setup["requests"]), "whole")
+
+
+def test_whole_prompts_with_the_recurrence_in_short_pieces(setup, monkeypatch):
+    """Prompts of a few dozen tokens already run the state-space recurrence in pieces (of 8 tokens), in a batch of unequal
+    requests too; the states the pieces leave are the ones that the single tokens after them start from."""
+    from hipinfer_b200.kernels import ops
+
+    monkeypatch.setattr(ops, "SSD_PIECE_TOKENS", 8)
+    _check(setup, tiny.plan_whole(setup["requests"]), "whole in pieces")
+    _check(setup, tiny.plan_tail_decode(setup["requests"], 5), "pieces then single tokens")
+    _check(setup, tiny.plan_mixed(setup["requests"], 11), "mixed in pieces")
 
 
 def test_last_tokens_one_by_one(setup):

@@ -129,11 +129,13 @@ def test_causal_convolution_carries_its_last_inputs(dtype, C, K):
 
 
 @pytest.mark.parametrize("H,P,N,G", [(4, 16, 8, 2), (3, 6, 7, 1), (2, 64, 128, 1), (6, 48, 48, 3), (1, 128, 16, 1), (2, 10, 5, 2)])
-def test_recurrence_against_the_plain_scan(H, P, N, G):
-    """Whole, in portions and token by token: the same bits (a token's arithmetic does not depend on where a portion
-    starts), and the plain scan's values. Head 0 hardly decays and token 0 is huge: it is still there 300 tokens on."""
+def test_recurrence_against_the_plain_scan(H, P, N, G, monkeypatch):
+    """Whole, in portions and token by token, each request in one walk: the same bits (a token's arithmetic does not depend
+    on where a portion starts), and the plain scan's values. Head 0 hardly decays and token 0 is huge: it is still there
+    300 tokens on."""
     from hipinfer_b200.kernels import ops
 
+    monkeypatch.setattr(ops, "SSD_PIECE_TOKENS", 0)
     T = 320
     x, B, C = rnd(T, H, P, seed=1), rnd(T, G, N, seed=2), rnd(T, G, N, seed=3)
     x[0] *= 30.0
@@ -158,6 +160,48 @@ def test_recurrence_against_the_plain_scan(H, P, N, G):
         outs.append(y.cpu())
     close(outs[0], want, torch.float32, "whole", tol=3e-5)
     assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+
+
+@pytest.mark.parametrize("piece", [4, 16, 64])
+@pytest.mark.parametrize("H,P,N,G", [(4, 16, 8, 2), (3, 6, 7, 1), (2, 64, 128, 1), (6, 48, 48, 3)])
+def test_recurrence_in_pieces(H, P, N, G, piece, monkeypatch):
+    """Long portions in pieces (each from zero, the starting states one after another, each again for y): three requests of
+    unequal length in one step, one of a single token, one that ends in the middle of a piece, each after a first portion
+    that left a state; against the plain scan and against the walk in one go, outputs and states. Head 0 hardly decays and
+    a request's first token is huge, so a starting state that was lost or decayed wrongly shows in every later piece."""
+    from hipinfer_b200.kernels import ops
+
+    first, lens = [5, 3, 2], [1, 3 * piece + piece // 2 + 1, 5 * piece]
+    total = [a + b for a, b in zip(first, lens)]
+    gen = lambda n, sd: (rnd(n, H, P, seed=sd), rnd(n, G, N, seed=sd + 1), rnd(n, G, N, seed=sd + 2), rnd(n, H, seed=sd + 3))
+    data = [gen(n, 10 * r) for r, n in enumerate(total)]
+    for x, *_ in data:
+        x[0] *= 30.0
+    dt_bias, d = rnd(H, seed=5), 1.0 + 0.5 * rnd(H, seed=6)
+    a_log = torch.linspace(-6.0, 1.0, H)
+    want = [plain.state_space_scan(x.double(), B.double(), C.double(), plain.softplus(dtr.double() + dt_bias.double()), a_log.double(),
+                                   d.double(), G).reshape(-1, H * P) for x, B, C, dtr in data]
+    rows = lambda part: (torch.cat([torch.cat([x.reshape(len(x), -1), B.reshape(len(x), -1), C.reshape(len(x), -1)], 1)[part(r)]
+                                    for r, (x, B, C, _) in enumerate(data)]).to(DEV),
+                         torch.cat([dtr[part(r)] for r, (*_, dtr) in enumerate(data)]).to(DEV))
+    res = {}
+    for label, size in (("one walk", 0), ("pieces", piece)):
+        monkeypatch.setattr(ops, "SSD_PIECE_TOKENS", size)
+        state = torch.zeros(4, H, N, P, dtype=torch.float32, device=DEV)
+        ys = []
+        for part, ln in ((lambda r: slice(0, first[r]), first), (lambda r: slice(first[r], None), lens)):
+            xbc, dtr = rows(part)
+            y = torch.empty(sum(ln), H * P, dtype=torch.float32, device=DEV)
+            ops.ssd_scan(xbc, dtr, dt_bias.to(DEV), a_log.to(DEV), d.to(DEV), state, batch_of(ln, slots=[3, 0, 2]), y, H, P, N, G)
+            ys.append(y.cpu())
+        res[label] = (ys[1], state.cpu())
+        t = 0
+        for r, n in enumerate(lens):
+            close(ys[1][t:t + n], want[r][first[r]:], torch.float32, f"{label}, request {r}", tol=3e-5)
+            t += n
+        assert float(state[1].abs().max()) == 0.0
+    close(res["pieces"][0], res["one walk"][0].double(), torch.float32, "pieces against one walk", tol=1e-5)
+    close(res["pieces"][1], res["one walk"][1].double(), torch.float32, "states", tol=1e-5)
 
 
 def test_recurrence_of_two_requests_in_one_step():
