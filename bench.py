@@ -607,16 +607,19 @@ def design_bench(a) -> int:
 
                 r["prefill_kernels"] = kernel_table(one_prefill)
                 runner._graphs.clear()          # graphs captured above hold programmatic edges; the table's step is captured anew
-                ids = [("kd", i) for i in range(8)]
-                first = [ops.sample(runner.step([StepEntry(rid, p, [PROMPT_LEN - 1])]), None, None, None)
-                         for rid, p in zip(ids, prompts(8, 1))]
-                tokens = torch.cat(first).contiguous()
-                entries = [StepEntry(rid, [0], [0]) for rid in ids]
-                r["decode_b8_kernels"] = kernel_table(
-                    lambda: ops.sample(runner.step(entries, device_tokens=tokens), None, None, None, out=tokens))
-                for rid in ids:
-                    runner.end(rid)
-                runner._graphs.clear()
+                for nb in (8, 64):
+                    if nb > max(batches):
+                        continue
+                    ids = [("kd", nb, i) for i in range(nb)]
+                    first = [ops.sample(runner.step([StepEntry(rid, p, [PROMPT_LEN - 1])]), None, None, None)
+                             for rid, p in zip(ids, prompts(nb, 1))]
+                    tokens = torch.cat(first).contiguous()
+                    entries = [StepEntry(rid, [0], [0]) for rid in ids]
+                    r[f"decode_b{nb}_kernels"] = kernel_table(
+                        lambda: ops.sample(runner.step(entries, device_tokens=tokens), None, None, None, out=tokens))
+                    for rid in ids:
+                        runner.end(rid)
+                    runner._graphs.clear()
             eng.close()
             del eng
             torch.cuda.empty_cache()

@@ -134,14 +134,95 @@ __global__ void __launch_bounds__(HS_THREADS) streams_update_norm_kernel(float* 
   }
 }
 
+// The same for rows of up to HS_THREADS * 4 * HS_KEEP columns (a multiple of four) and a stream count known to the compiler:
+// four columns a load, and u stays in registers between the two passes, so a row is read once and written once.
+constexpr int HS_KEEP = 4;
+
+template <typename TW, typename TO, int S>
+__global__ void __launch_bounds__(HS_THREADS) streams_update_norm_vec_kernel(float* __restrict__ x, const float* __restrict__ y,
+                                                                             const float* __restrict__ b, const float* __restrict__ M,
+                                                                             float m, const float* __restrict__ a_next,
+                                                                             const TW* __restrict__ w_next, TO* __restrict__ out,
+                                                                             int W, float eps) {
+  __shared__ float sh[32];
+  hb_pdl_launch();
+  float ca[S], cb[S], cm[S][S];
+#pragma unroll
+  for (int s = 0; s < S; s++) {
+    ca[s] = a_next ? a_next[s] : 1.f;
+    cb[s] = b ? m * b[s] : m;
+#pragma unroll
+    for (int t = 0; t < S; t++) cm[s][t] = M ? M[s * S + t] : (s == t ? 1.f : 0.f);
+  }
+  hb_pdl_wait();
+  const int r = blockIdx.x;
+  float* row = x + (size_t)r * S * W;
+  float4 uu[HS_KEEP];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < HS_KEEP; k++) {
+    const int i = (k * HS_THREADS + threadIdx.x) * 4;
+    uu[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (i < W) {
+      float4 old[S];
+#pragma unroll
+      for (int s = 0; s < S; s++) old[s] = *(const float4*)(row + (size_t)s * W + i);
+      const float4 yy = *(const float4*)(y + (size_t)r * W + i);
+      float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int to = 0; to < S; to++) {
+        float4 v = make_float4(cb[to] * yy.x, cb[to] * yy.y, cb[to] * yy.z, cb[to] * yy.w);
+#pragma unroll
+        for (int s = 0; s < S; s++) {
+          v.x = fmaf(cm[s][to], old[s].x, v.x);
+          v.y = fmaf(cm[s][to], old[s].y, v.y);
+          v.z = fmaf(cm[s][to], old[s].z, v.z);
+          v.w = fmaf(cm[s][to], old[s].w, v.w);
+        }
+        *(float4*)(row + (size_t)to * W + i) = v;
+        u.x = fmaf(ca[to], v.x, u.x);
+        u.y = fmaf(ca[to], v.y, u.y);
+        u.z = fmaf(ca[to], v.z, u.z);
+        u.w = fmaf(ca[to], v.w, u.w);
+      }
+      uu[k] = u;
+      ss = fmaf(u.x, u.x, ss);
+      ss = fmaf(u.y, u.y, ss);
+      ss = fmaf(u.z, u.z, ss);
+      ss = fmaf(u.w, u.w, ss);
+    }
+  }
+  const float f = rsqrtf(hb_block_sum(ss, sh) / (float)W + eps);
+#pragma unroll
+  for (int k = 0; k < HS_KEEP; k++) {
+    const int i = (k * HS_THREADS + threadIdx.x) * 4;
+    if (i < W) {
+      const float4 wv = hb_load4(w_next + i);
+      hb_store4(out + (size_t)r * W + i, make_float4(uu[k].x * f * wv.x, uu[k].y * f * wv.y, uu[k].z * f * wv.z, uu[k].w * f * wv.w));
+    }
+  }
+}
+
 HB_EXPORT int hb_streams_update_norm(float* x, const float* y, const float* b, const float* M, float m, const float* a_next,
                                      const void* w_next, int w_dt, void* out, int o_dt, int T, int S, int W, float eps,
                                      cudaStream_t s) {
   if (T <= 0) return 0;
   if (S < 1 || S > HS_MAX) HB_FAIL("hb_streams_update_norm: %d streams (1 to %d are supported)", S, HS_MAX);
-  HB_DISPATCH_2(w_dt, o_dt, "hb_streams_update_norm",
-                (hb_launch(streams_update_norm_kernel<TA, TB>, T, HS_THREADS, 0, s, x, y, b, M, m, a_next, (const TA*)w_next,
-                           (TB*)out, S, W, eps)));
+  const bool vec = W % 4 == 0 && W <= HS_THREADS * 4 * HS_KEEP && S <= 4 &&
+                   !(((uintptr_t)x | (uintptr_t)y | (uintptr_t)out | (uintptr_t)w_next) & 15);
+#define HS_VEC(SS)                                                                                                    \
+  HB_DISPATCH_2(w_dt, o_dt, "hb_streams_update_norm",                                                                 \
+                (hb_launch(streams_update_norm_vec_kernel<TA, TB, SS>, T, HS_THREADS, 0, s, x, y, b, M, m, a_next,    \
+                           (const TA*)w_next, (TB*)out, W, eps)))
+  if (vec && S == 1) HS_VEC(1);
+  else if (vec && S == 2) HS_VEC(2);
+  else if (vec && S == 3) HS_VEC(3);
+  else if (vec && S == 4) HS_VEC(4);
+  else
+    HB_DISPATCH_2(w_dt, o_dt, "hb_streams_update_norm",
+                  (hb_launch(streams_update_norm_kernel<TA, TB>, T, HS_THREADS, 0, s, x, y, b, M, m, a_next, (const TA*)w_next,
+                             (TB*)out, S, W, eps)));
+#undef HS_VEC
   HB_CHECK_LAUNCH("hb_streams_update_norm");
   return 0;
 }

@@ -8,6 +8,11 @@
 // Few rows (decoding): no sorting, nothing on the host
 //   moe_gate_up_rows_kernel a block per ((row, choice), tile of the expert's hidden rows): act [T * top][F]
 //   moe_down_rows_kernel    a block per (row, tile of output columns): the choices' results summed in their order
+// Some rows (decoding in a batch): the pairs sorted by expert on the device, then
+//   moe_grouped_kernel      a block per (expert, tile of output features): the expert's weights are read once for all of
+//   moe_grouped_mma_kernel  its rows (a round of them at a time), for the gate/up product and for the down product;
+//                           nothing on the host, so the step replays from a CUDA graph. The second is the bfloat16 form on
+//                           warp MMAs, the first takes any element types and sizes
 // Many rows (prompt portions): the (row, choice) pairs are sorted by expert, so that each expert's rows are one
 // contiguous block that an ordinary product takes
 //   moe_sort_kernel         offsets [E + 1], pos [pair] -> sorted row, src [sorted row] -> pair
@@ -170,6 +175,226 @@ HB_EXPORT int hb_moe_down_rows(const void* act, int a_dt, const void* wd, int w_
     hb_launch(kern, grid, dim3(MG_THREADS), smem, s, (const TA*)act, (const TB*)wd, expert, y, ldy, W, F, top, vec);
   } while (0));
   HB_CHECK_LAUNCH("hb_moe_down_rows");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Some rows: one product kernel over all experts' blocks of sorted rows.
+//   out[r][n] = sum_k w[e][n][k] a[row(r)][k]   for offsets[e] <= r < offsets[e + 1], e = blockIdx.y
+// row(r) = src[r] / top where src is given (the step's input rows, gathered on the fly), else r. A warp owns MX_NW output
+// features and MX_RB rows at a time: a weight row comes from memory once a round of rows, the rows wait in shared memory in
+// their own element type, K in segments of KS. A (row, feature) sum runs in the same order whatever else is in the round.
+// ---------------------------------------------------------------------------------------------------------------------
+constexpr int MX_THREADS = 256, MX_RB = 8, MX_NW = 4, MX_TILE = (MX_THREADS / 32) * MX_NW;
+
+template <typename T> struct MxVec4;
+template <> struct MxVec4<float> { using type = float4; };
+template <> struct MxVec4<__nv_bfloat16> { using type = uint2; };
+
+// One round: R rows (the first nr of them live) against the block's MX_TILE output features.
+template <typename TA, typename TW, int R>
+__device__ __forceinline__ void mx_round(const TA* __restrict__ a, long lda, const int* mx_row, int nr, const TW* __restrict__ we,
+                                         float* __restrict__ out, TA* rows, int g0, int n0, int Nout, int K, int KS, int vec) {
+  using V4 = typename MxVec4<TA>::type;
+  const int tid = threadIdx.x, lane = tid & 31;
+  float acc[MX_NW][R];
+#pragma unroll
+  for (int q = 0; q < MX_NW; q++)
+#pragma unroll
+    for (int r = 0; r < R; r++) acc[q][r] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += KS) {
+    const int kn = min(KS, K - k0);
+    __syncthreads();                                        // the segment before has been read; mx_row is written
+    if (vec) {
+      const int per = kn >> 2;
+      for (int r = 0; r < nr; r++) {
+        const TA* ar = a + (size_t)mx_row[r] * lda + k0;
+#pragma unroll 4
+        for (int i = tid; i < per; i += MX_THREADS) *(V4*)(rows + (size_t)r * KS + 4 * i) = *(const V4*)(ar + 4 * i);
+      }
+    } else {
+      for (int r = 0; r < nr; r++) {
+        const TA* ar = a + (size_t)mx_row[r] * lda + k0;
+        for (int i = tid; i < kn; i += MX_THREADS) rows[(size_t)r * KS + i] = ar[i];
+      }
+    }
+    __syncthreads();
+    if (vec) {
+#pragma unroll 2
+      for (int i = lane * 4; i < kn; i += 128) {
+        float4 wv[MX_NW];
+#pragma unroll
+        for (int q = 0; q < MX_NW; q++)
+          wv[q] = n0 + q < Nout ? hb_load4(we + (size_t)(n0 + q) * K + k0 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+          const float4 av = hb_load4(rows + (size_t)r * KS + i);
+#pragma unroll
+          for (int q = 0; q < MX_NW; q++) {
+            acc[q][r] = fmaf(wv[q].x, av.x, acc[q][r]);
+            acc[q][r] = fmaf(wv[q].y, av.y, acc[q][r]);
+            acc[q][r] = fmaf(wv[q].z, av.z, acc[q][r]);
+            acc[q][r] = fmaf(wv[q].w, av.w, acc[q][r]);
+          }
+        }
+      }
+    } else {
+      for (int i = lane; i < kn; i += 32) {
+        float wv[MX_NW];
+#pragma unroll
+        for (int q = 0; q < MX_NW; q++) wv[q] = n0 + q < Nout ? hb_to_float(we[(size_t)(n0 + q) * K + k0 + i]) : 0.f;
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+          const float av = hb_to_float(rows[(size_t)r * KS + i]);
+#pragma unroll
+          for (int q = 0; q < MX_NW; q++) acc[q][r] = fmaf(wv[q], av, acc[q][r]);
+        }
+      }
+    }
+  }
+  // rows beyond nr hold whatever shared memory held: their sums are never stored
+#pragma unroll
+  for (int q = 0; q < MX_NW; q++)
+#pragma unroll
+    for (int r = 0; r < R; r++) {
+      const float v = hb_warp_sum(acc[q][r]);
+      if (lane == 0 && n0 + q < Nout && r < nr) out[(size_t)(g0 + r) * Nout + n0 + q] = v;
+    }
+}
+
+template <typename TA, typename TW>
+__global__ void __launch_bounds__(MX_THREADS) moe_grouped_kernel(const TA* __restrict__ a, long lda, const int* __restrict__ src,
+                                                                 int top, const TW* __restrict__ w, const int* __restrict__ offsets,
+                                                                 float* __restrict__ out, int Nout, int K, int KS, int vec) {
+  extern __shared__ __align__(16) unsigned char mx_raw[];
+  __shared__ int mx_row[MX_RB];
+  TA* rows = (TA*)mx_raw;                                   // [MX_RB][KS]
+  hb_pdl_launch();
+  hb_pdl_wait();
+  const int e = blockIdx.y, lo = offsets[e], hi = offsets[e + 1];
+  if (lo >= hi) return;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int n0 = blockIdx.x * MX_TILE + warp * MX_NW;
+  const TW* we = w + (size_t)e * Nout * K;
+  for (int g0 = lo; g0 < hi; g0 += MX_RB) {
+    const int nr = min(MX_RB, hi - g0);
+    __syncthreads();                                        // the round before has read its row numbers
+    if (tid < nr) mx_row[tid] = src ? src[g0 + tid] / top : g0 + tid;
+    // a round of few rows does the sums of few rows; which form a row meets changes nothing in its sums
+    if (nr == 1) mx_round<TA, TW, 1>(a, lda, mx_row, nr, we, out, rows, g0, n0, Nout, K, KS, vec);
+    else if (nr == 2) mx_round<TA, TW, 2>(a, lda, mx_row, nr, we, out, rows, g0, n0, Nout, K, KS, vec);
+    else if (nr <= 4) mx_round<TA, TW, 4>(a, lda, mx_row, nr, we, out, rows, g0, n0, Nout, K, KS, vec);
+    else mx_round<TA, TW, MX_RB>(a, lda, mx_row, nr, we, out, rows, g0, n0, Nout, K, KS, vec);
+  }
+}
+
+// The same product on warp MMAs (bfloat16 rows and weights, K a multiple of 32). The weights are the MMA's row operand,
+// 16 output features a warp, and come straight from memory: a lane reads 8 consecutive k of feature g and of feature
+// g + 8 (16 bytes each) per block of 32 k; the rows are the column operand, 8 a tile, up to 4 tiles a round, from shared
+// memory in segments of MM_KS k (twice and four times as many where a round has at most 16 or 8 rows). Inside a block of 32 k the lanes' k are dealt to the MMA's k slots in another order than
+// memory's, the same for both operands, which a sum over k does not see. 32-bit accumulation; a (row, feature) sum does
+// not depend on the other rows of the round.
+constexpr int MM_THREADS = 128, MM_KS = 1024, MM_LD = MM_KS + 32, MM_ROWS = 32, MM_TILE = 16 * (MM_THREADS / 32);
+
+__device__ __forceinline__ void mm_mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int NT>
+__device__ __forceinline__ void mm_round(const __nv_bfloat16* __restrict__ a, long lda, const int* mm_row, int nr,
+                                         const __nv_bfloat16* __restrict__ we, float* __restrict__ out, __nv_bfloat16* rows, int g0,
+                                         int n0, int Nout, int K) {
+  constexpr int KS = MM_KS * 4 / NT, LD = KS + 32;           // the same shared memory holds fewer rows of more k
+  const int tid = threadIdx.x, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  float acc[NT][4];
+#pragma unroll
+  for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+    for (int i = 0; i < 4; i++) acc[nt][i] = 0.f;
+  // features past the end read the last feature's weights; their sums are not stored
+  const __nv_bfloat16* wa = we + (size_t)min(n0 + g, Nout - 1) * K + t * 8;
+  const __nv_bfloat16* wb = we + (size_t)min(n0 + g + 8, Nout - 1) * K + t * 8;
+  for (int k0 = 0; k0 < K; k0 += KS) {
+    const int kn = min(KS, K - k0), per = kn >> 3;
+    __syncthreads();                                        // the segment before has been read; mm_row is written
+    for (int r = 0; r < nr; r++) {
+      const __nv_bfloat16* ar = a + (size_t)mm_row[r] * lda + k0;
+#pragma unroll 4
+      for (int i = tid; i < per; i += MM_THREADS) *(uint4*)(rows + (size_t)r * LD + 8 * i) = *(const uint4*)(ar + 8 * i);
+    }
+    __syncthreads();
+#pragma unroll 4
+    for (int kb = 0; kb < kn; kb += 32) {
+      const uint4 A0 = *(const uint4*)(wa + k0 + kb), A1 = *(const uint4*)(wb + k0 + kb);
+#pragma unroll
+      for (int nt = 0; nt < NT; nt++) {
+        // rows past nr hold whatever shared memory held: a row is a column of the MMA, and its sums are not stored
+        const uint4 B = *(const uint4*)(rows + (size_t)(nt * 8 + g) * LD + kb + t * 8);
+        mm_mma(acc[nt], A0.x, A1.x, A0.y, A1.y, B.x, B.y);
+        mm_mma(acc[nt], A0.z, A1.z, A0.w, A1.w, B.z, B.w);
+      }
+    }
+  }
+#pragma unroll
+  for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const int r = nt * 8 + 2 * t + (i & 1), n = n0 + g + (i >> 1) * 8;
+      if (r < nr && n < Nout) out[(size_t)(g0 + r) * Nout + n] = acc[nt][i];
+    }
+}
+
+__global__ void __launch_bounds__(MM_THREADS) moe_grouped_mma_kernel(const __nv_bfloat16* __restrict__ a, long lda,
+                                                                     const int* __restrict__ src, int top,
+                                                                     const __nv_bfloat16* __restrict__ w,
+                                                                     const int* __restrict__ offsets, float* __restrict__ out,
+                                                                     int Nout, int K) {
+  extern __shared__ __align__(16) unsigned char mx_raw[];
+  __shared__ int mm_row[MM_ROWS];
+  __nv_bfloat16* rows = (__nv_bfloat16*)mx_raw;             // [MM_ROWS][MM_LD], or half the rows of twice the k, or a quarter of four times
+  hb_pdl_launch();
+  hb_pdl_wait();
+  const int e = blockIdx.y, lo = offsets[e], hi = offsets[e + 1];
+  if (lo >= hi) return;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int n0 = blockIdx.x * MM_TILE + warp * 16;
+  const __nv_bfloat16* we = w + (size_t)e * Nout * K;
+  for (int g0 = lo; g0 < hi; g0 += MM_ROWS) {
+    const int nr = min(MM_ROWS, hi - g0);
+    __syncthreads();                                        // the round before has read its row numbers
+    if (tid < nr) mm_row[tid] = src ? src[g0 + tid] / top : g0 + tid;
+    if (nr <= 8) mm_round<1>(a, lda, mm_row, nr, we, out, rows, g0, n0, Nout, K);
+    else if (nr <= 16) mm_round<2>(a, lda, mm_row, nr, we, out, rows, g0, n0, Nout, K);
+    else mm_round<4>(a, lda, mm_row, nr, we, out, rows, g0, n0, Nout, K);
+  }
+}
+
+HB_EXPORT int hb_moe_grouped(const void* a, int a_dt, long lda, const int* src, int top, const void* w, int w_dt,
+                             const int* offsets, float* out, int E, int Nout, int K, cudaStream_t s) {
+  if (E <= 0 || Nout <= 0 || K <= 0) return 0;
+  if (E > 65535) HB_FAIL("hb_moe_grouped: %d experts are too many for this kernel", E);
+  if (a_dt == HB_BF16 && w_dt == HB_BF16 && K % 32 == 0 && lda % 8 == 0 && !(((uintptr_t)a | (uintptr_t)w) & 15)) {
+    const size_t smem = (size_t)MM_ROWS * MM_LD * sizeof(__nv_bfloat16);
+    cudaFuncSetAttribute(moe_grouped_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    hb_launch(moe_grouped_mma_kernel, dim3((Nout + MM_TILE - 1) / MM_TILE, E), dim3(MM_THREADS), smem, s,
+              (const __nv_bfloat16*)a, lda, src, top, (const __nv_bfloat16*)w, offsets, out, Nout, K);
+    HB_CHECK_LAUNCH("hb_moe_grouped");
+    return 0;
+  }
+  const int esz = a_dt == HB_F32 ? 4 : 2;
+  const int vec = (K % 4 == 0 && lda % 4 == 0 && ((uintptr_t)a & 15) == 0 && ((uintptr_t)w & 15) == 0) ? 1 : 0;
+  const int cap = (64 * 1024 / (MX_RB * esz)) & ~3;        // a segment's elements a row
+  const int KS = K < cap ? ((K + 3) & ~3) : cap;
+  const size_t smem = (size_t)MX_RB * KS * esz;
+  dim3 grid((Nout + MX_TILE - 1) / MX_TILE, E);
+  HB_DISPATCH_2(a_dt, w_dt, "hb_moe_grouped", do {
+    auto kern = moe_grouped_kernel<TA, TB>;
+    if (smem > 40 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    hb_launch(kern, grid, dim3(MX_THREADS), smem, s, (const TA*)a, lda, src, top, (const TB*)w, offsets, out, Nout, K, KS, vec);
+  } while (0));
+  HB_CHECK_LAUNCH("hb_moe_grouped");
   return 0;
 }
 

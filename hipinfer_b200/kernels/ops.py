@@ -70,6 +70,7 @@ _SIGS = {
         "hb_moe_gate_up_rows": [_p, _i, _l, _p, _i, _p, _p, _p, _i, _i, _i, _i, _p],
         "hb_moe_down_rows": [_p, _i, _p, _i, _p, _p, _l, _i, _i, _i, _i, _p],
         "hb_moe_sort": [_p, _p, _p, _p, _i, _i, _p],
+        "hb_moe_grouped": [_p, _i, _l, _p, _i, _p, _i, _p, _p, _i, _i, _i, _p],
         "hb_moe_gather": [_p, _i, _l, _p, _p, _i, _i, _i, _p],
         "hb_moe_act": [_p, _p, _p, _p, _i, _i, _i, _p],
         "hb_moe_combine": [_p, _p, _p, _l, _i, _i, _i, _p],
@@ -1188,6 +1189,21 @@ def moe_sort(expert: torch.Tensor, n_experts: int):
     _call("hybrid", "hb_moe_sort", expert.data_ptr(), offsets.data_ptr(), pos.data_ptr(), src.data_ptr(), pairs, int(n_experts),
           _stream())
     return offsets, pos, src
+
+
+def moe_grouped(a: torch.Tensor, src: Optional[torch.Tensor], top: int, w: torch.Tensor, offsets: torch.Tensor,
+                out: torch.Tensor) -> torch.Tensor:
+    """out[r] = w[e] a[row(r)] for the sorted rows r of every expert e (offsets[e] <= r < offsets[e + 1]); row(r) is
+    src[r] // top where src is given (the step's input rows), else r. w [E, Nout, K]; out float32 [sorted rows, Nout].
+    An expert's weights are read once for all of its rows; nothing is read by the host."""
+    _need_cuda(a, w, offsets, out)
+    _rows_contiguous(a, "moe_grouped in")
+    E, Nout, K = w.shape
+    assert w.is_contiguous() and a.shape[1] == K and out.dtype == torch.float32 and out.is_contiguous() and out.shape[1] == Nout
+    assert offsets.numel() == E + 1 and offsets.dtype == torch.int32 and (src is None or src.dtype == torch.int32)
+    _call("hybrid", "hb_moe_grouped", a.data_ptr(), _dt(a), a.stride(0), _ptr(src), int(top), w.data_ptr(), _dt(w),
+          offsets.data_ptr(), out.data_ptr(), E, Nout, K, _stream())
+    return out
 
 
 def moe_gather(xn: torch.Tensor, src: torch.Tensor, top: int) -> torch.Tensor:

@@ -6,9 +6,10 @@ runs `top`.
     out = sum over the chosen e of Wdown_e (silu(Wgate_e v) * (Wup_e v)),  v = s_e h     the score multiplies the INPUT
 
 Without biases Wgate_e (s h) = s (Wgate_e h): the products run on h and the score enters the activation in 32-bit.
-Steps of single rows (decoding) run row by row on the device alone (csrc/moe.cu), so they replay from a CUDA graph; a
-step with prompt portions sorts its (row, choice) pairs by expert and gives each expert's block of rows to the ordinary
-products (the tensor-core kernels in bfloat16), for which the host reads the experts' row counts once a layer.
+Steps of single rows (decoding) run on the device alone (csrc/moe.cu), so they replay from a CUDA graph: a few rows one
+by one, more of them sorted by expert so that an expert's weights are read once for all of its rows. A step with prompt
+portions sorts its (row, choice) pairs by expert and gives each expert's block of rows to the ordinary products (the
+tensor-core kernels in bfloat16), for which the host reads the experts' row counts once a layer.
 
 params: hidden_size, experts, top, expert_size, router_name (default "mlp.router"), expert_prefix (default "mlp.e": expert
 i's tensors are <expert_prefix><i>.gate / .up / .down).
@@ -22,7 +23,8 @@ from ..weights import ParamSpec
 from . import planes
 from .registry import Part, register_part, to_compute
 
-SORTED_MIN_PAIRS = 64     # fewer (row, choice) pairs than this always run row by row
+SORTED_MIN_PAIRS = 64     # fewer (row, choice) pairs than this never go to the ordinary products
+GROUPED_MIN_PAIRS = 20    # fewer than this run row by row; from here on an expert's rows share one pass over its weights
 
 
 class RoutedFF(Part):
@@ -67,10 +69,20 @@ class RoutedFF(Part):
     def forward(self, xn, x, batch):
         T, top, F = xn.shape[0], self.top, self.inter
         expert, score = ops.moe_route(xn, self.router, top)
-        if getattr(batch, "max_q_len", 1) <= 1 or T * top < SORTED_MIN_PAIRS:
+        if T * top < GROUPED_MIN_PAIRS:
             ops.moe_rows(xn, self.wgu, self.wdown, expert, score, x)
             return None
         offsets, pos, src = ops.moe_sort(expert, self.experts)
+        if getattr(batch, "max_q_len", 1) <= 1 or T * top < SORTED_MIN_PAIRS:
+            gu = torch.empty(T * top, 2 * F, dtype=torch.float32, device=xn.device)
+            ops.moe_grouped(xn, src, top, self.wgu, offsets, gu)
+            act = torch.empty(T * top, F, dtype=self.ctx.dtype, device=xn.device)
+            ops.moe_act(gu, src, score, act)
+            planes.record(batch, "activation", act)
+            ys = torch.empty(T * top, self.hidden, dtype=torch.float32, device=xn.device)
+            ops.moe_grouped(act, None, 1, self.wdown, offsets, ys)
+            ops.moe_combine(ys, pos, x, top)
+            return None
         xs = ops.moe_gather(xn, src, top)
         bounds = offsets.tolist()                      # the one read by the host: how many rows each expert has
         gu = torch.empty(T * top, 2 * F, dtype=torch.float32, device=xn.device)

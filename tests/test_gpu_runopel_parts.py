@@ -45,7 +45,7 @@ def batch_of(lengths, ctx=None, slots=None):
 
 # ------------------------------------------------------------------------------------------ residual streams
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("S,W", [(1, 50), (2, 192), (3, 64), (8, 1000)])
+@pytest.mark.parametrize("S,W", [(1, 50), (2, 192), (3, 64), (8, 1000), (1, 128), (2, 2048), (4, 4096), (2, 4100)])
 def test_streams_read_norm_and_write_back(dtype, S, W):
     from hipinfer_b200.kernels import ops
 
@@ -254,17 +254,23 @@ def _routed(dtype, W, F, E, top, seed=0):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("W,F,E,top,T", [(64, 32, 5, 2, 9), (50, 22, 3, 3, 7), (128, 96, 16, 4, 200), (192, 96, 8, 1, 130), (48, 40, 1, 1, 5)])
-def test_routed_feed_forward_row_by_row_and_sorted(dtype, W, F, E, top, T):
-    """The scores multiply the experts' inputs and are not renormalised; single rows (no sorting) and portions (sorted by
-    expert, an ordinary product per expert) give the plain sum."""
+@pytest.mark.parametrize("W,F,E,top,T", [(64, 32, 5, 2, 9), (50, 22, 3, 3, 7), (128, 96, 16, 4, 200), (192, 96, 8, 1, 130), (48, 40, 1, 1, 5),
+                                         (2200, 24, 3, 2, 19), (4360, 16, 2, 1, 11), (2112, 72, 4, 2, 40), (96, 160, 3, 2, 30)])
+def test_routed_feed_forward_row_by_row_grouped_and_sorted(dtype, W, F, E, top, T, monkeypatch):
+    """The scores multiply the experts' inputs and are not renormalised; single rows one by one (no sorting), single rows
+    grouped by expert (rounds of up to 8, 16 and 32 rows, rows wider than a segment of shared memory, experts without a
+    row, feature counts that end inside a tile; widths the warp-MMA form takes and widths it does not) and
+    portions (sorted by expert, an ordinary product per expert) give the plain sum."""
+    from hipinfer_b200.parts import routed_ff
+
     part, w = _routed(dtype, W, F, E, top)
     h = (rnd(T, W, seed=50) * 1.5).to(dtype)
     want = plain.routed_ff(h.double(), w, E, top)
-    for q_len in (1, T):
+    for what, q_len, grouped_from in (("one by one", 1, 10 ** 9), ("grouped", 1, 1), ("sorted", T, 1)):
+        monkeypatch.setattr(routed_ff, "GROUPED_MIN_PAIRS", grouped_from)
         y = torch.full((T, W), 0.25, dtype=torch.float32, device=DEV)            # the result is ADDED
         part.forward(h.to(DEV), y, SimpleNamespace(max_q_len=q_len, dump=None))
-        close(y - 0.25, want, dtype, f"steps of {q_len} rows")
+        close(y - 0.25, want, dtype, what)
 
 
 def test_router_ties_go_to_the_lower_index():
