@@ -136,7 +136,11 @@ __device__ __forceinline__ void ss_cp4(float* dst, const float* src) {
 
 template <int DPT> struct SsdThreads { static constexpr int MAX = DPT <= 8 ? 1024 : DPT <= 32 ? 512 : 256; };
 
-template <int DPT, typename TW, int MODE>
+// FAST: N == DPT * KS with 16-byte aligned rows of multiples of four. A thread then holds the DPT CONTIGUOUS state channels
+// ks * DPT .. of its value channel and reads their dt B and C four at a time (B and C lie in shared memory with 4 floats of
+// padding after every DPT, so that the KS slices fall on different banks); no bounds are checked and every offset is a
+// constant. Otherwise (any sizes) a thread holds every KS-th state channel.
+template <int DPT, typename TW, int MODE, bool FAST>
 __global__ void __launch_bounds__(SsdThreads<DPT>::MAX, 1) ssd_scan_kernel(SsdArgs A) {
   extern __shared__ __align__(16) float ssm[];
   hb_pdl_launch();
@@ -152,12 +156,14 @@ __global__ void __launch_bounds__(SsdThreads<DPT>::MAX, 1) ssd_scan_kernel(SsdAr
   if (MODE != SS_WHOLE && j_begin >= len) return;
   float* S_g = MODE == SS_WHOLE ? A.state + ((size_t)A.slot[r] * H + h) * N * P
                                 : A.piece_state + (((size_t)r * A.pieces + blockIdx.z) * H + h) * N * P;
-  // a token's row in shared memory: [B -> dt B (N) | C (N) | x (P) | dt_raw -> decay (1) | pad], two chunks deep
-  const int RW = ((2 * N + P + 1 + 3) / 4) * 4;
+  // a token's row in shared memory: [B -> dt B (NQ) | C (NQ) | x (P) | dt_raw -> decay (1) | pad], two chunks deep
+  const int NQ = FAST ? N + 4 * KS : N;
+  const int RW = ((2 * NQ + P + 1 + 3) / 4) * 4;
+  auto pidx = [&](int n) { return FAST ? n + (n / DPT) * 4 : n; };
   float S[DPT];
 #pragma unroll
   for (int i = 0; i < DPT; i++) {
-    const int n = i * KS + ks;
+    const int n = FAST ? ks * DPT + i : i * KS + ks;
     S[i] = (MODE != SS_PIECE_LOCAL && live && n < N) ? S_g[(size_t)n * P + p] : 0.f;
   }
   float decays = 1.f;
@@ -173,9 +179,9 @@ __global__ void __launch_bounds__(SsdThreads<DPT>::MAX, 1) ssd_scan_kernel(SsdAr
       for (int i = tid; i < n * per; i += nthr) {
         const int j = i / per, c = i - j * per;
         const float* row = A.xbc + (size_t)(t0 + c0 + j) * A.ldx;
-        if (c < cn) ss_cp16(st + j * RW + 4 * c, row + HP + g * N + 4 * c);
-        else if (c < 2 * cn) ss_cp16(st + j * RW + N + 4 * (c - cn), row + HP + GN + g * N + 4 * (c - cn));
-        else ss_cp16(st + j * RW + 2 * N + 4 * (c - 2 * cn), row + h * P + 4 * (c - 2 * cn));
+        if (c < cn) ss_cp16(st + j * RW + pidx(4 * c), row + HP + g * N + 4 * c);
+        else if (c < 2 * cn) ss_cp16(st + j * RW + NQ + pidx(4 * (c - cn)), row + HP + GN + g * N + 4 * (c - cn));
+        else ss_cp16(st + j * RW + 2 * NQ + 4 * (c - 2 * cn), row + h * P + 4 * (c - 2 * cn));
       }
     } else {
       const int per = 2 * N + P;
@@ -186,7 +192,7 @@ __global__ void __launch_bounds__(SsdThreads<DPT>::MAX, 1) ssd_scan_kernel(SsdAr
         ss_cp4(st + j * RW + c, src);
       }
     }
-    for (int j = tid; j < n; j += nthr) ss_cp4(st + j * RW + 2 * N + P, A.dt + (size_t)(t0 + c0 + j) * A.lddt + h);
+    for (int j = tid; j < n; j += nthr) ss_cp4(st + j * RW + 2 * NQ + P, A.dt + (size_t)(t0 + c0 + j) * A.lddt + h);
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
   if (len > j_begin) fetch(0, j_begin);
@@ -205,34 +211,61 @@ __global__ void __launch_bounds__(SsdThreads<DPT>::MAX, 1) ssd_scan_kernel(SsdAr
     for (int i = tid; i < n * N; i += nthr) {
       const int j = i / N, c = i - j * N;
       float* row = st + j * RW;
-      const float zz = row[2 * N + P] + dtb;
+      const float zz = row[2 * NQ + P] + dtb;
       const float dt = fmaxf(zz, 0.f) + log1pf(expf(-fabsf(zz)));
-      row[c] *= dt;
+      row[pidx(c)] *= dt;
     }
     __syncthreads();
     for (int j = tid; j < n; j += nthr) {
       float* row = st + j * RW;
-      const float zz = row[2 * N + P] + dtb;
+      const float zz = row[2 * NQ + P] + dtb;
       const float dt = fmaxf(zz, 0.f) + log1pf(expf(-fabsf(zz)));
-      row[2 * N + P] = expf(neg_a * dt);
+      row[2 * NQ + P] = expf(neg_a * dt);
     }
     __syncthreads();
     for (int j = 0; j < n; j++) {
       const float* row = st + j * RW;
-      const float xv = live ? row[2 * N + p] : 0.f;
-      const float a = row[2 * N + P];
+      const float xv = live ? row[2 * NQ + p] : 0.f;
+      const float a = row[2 * NQ + P];
       const float* Bj = row;
-      const float* Cj = row + N;
+      const float* Cj = row + NQ;
       if (MODE == SS_PIECE_LOCAL) {
         decays *= a;
+        if constexpr (FAST) {
+          const int sb = ks * (DPT + 4);
 #pragma unroll
-        for (int i = 0; i < DPT; i++) {
-          const int n0 = i * KS + ks;
-          if (n0 < N) S[i] = fmaf(a, S[i], Bj[n0] * xv);
+          for (int i = 0; i < DPT; i += 4) {
+            const float4 b4 = *(const float4*)(Bj + sb + i);
+            S[i] = fmaf(a, S[i], b4.x * xv);
+            S[i + 1] = fmaf(a, S[i + 1], b4.y * xv);
+            S[i + 2] = fmaf(a, S[i + 2], b4.z * xv);
+            S[i + 3] = fmaf(a, S[i + 3], b4.w * xv);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < DPT; i++) {
+            const int n0 = i * KS + ks;
+            if (n0 < N) S[i] = fmaf(a, S[i], Bj[n0] * xv);
+          }
         }
         continue;
       }
       float o = 0.f, o2 = 0.f;
+      if constexpr (FAST) {
+        const int sb = ks * (DPT + 4);
+#pragma unroll
+        for (int i = 0; i < DPT; i += 4) {
+          const float4 b4 = *(const float4*)(Bj + sb + i), c4 = *(const float4*)(Cj + sb + i);
+          S[i] = fmaf(a, S[i], b4.x * xv);
+          S[i + 1] = fmaf(a, S[i + 1], b4.y * xv);
+          S[i + 2] = fmaf(a, S[i + 2], b4.z * xv);
+          S[i + 3] = fmaf(a, S[i + 3], b4.w * xv);
+          o = fmaf(S[i], c4.x, o);
+          o2 = fmaf(S[i + 1], c4.y, o2);
+          o = fmaf(S[i + 2], c4.z, o);
+          o2 = fmaf(S[i + 3], c4.w, o2);
+        }
+      } else
 #pragma unroll
       for (int i = 0; i < DPT; i += 2) {
         const int n0 = i * KS + ks, n1 = n0 + KS;
@@ -254,7 +287,7 @@ __global__ void __launch_bounds__(SsdThreads<DPT>::MAX, 1) ssd_scan_kernel(SsdAr
   if (MODE == SS_PIECE_OUT) return;
 #pragma unroll
   for (int i = 0; i < DPT; i++) {
-    const int n = i * KS + ks;
+    const int n = FAST ? ks * DPT + i : i * KS + ks;
     if (live && n < N) S_g[(size_t)n * P + p] = S[i];
   }
   if (MODE == SS_PIECE_LOCAL && tid == 0) A.piece_decay[((size_t)r * A.pieces + blockIdx.z) * H + h] = decays;
@@ -273,11 +306,24 @@ __global__ void __launch_bounds__(256) ssd_carry_kernel(SsdArgs A) {
   const int pieces = (len + A.L - 1) / A.L;
   float* slot = A.state + (size_t)A.slot[r] * A.H * NP + e;
   float carry = *slot;
-  for (int c = 0; c < pieces; c++) {
-    float* ps = A.piece_state + ((size_t)r * A.pieces + c) * A.H * NP + e;
-    const float own = *ps;
-    *ps = carry;
-    carry = fmaf(A.piece_decay[((size_t)r * A.pieces + c) * A.H + h], carry, own);
+  float* ps = A.piece_state + (size_t)r * A.pieces * A.H * NP + e;
+  const float* pd = A.piece_decay + (size_t)r * A.pieces * A.H + h;
+  const size_t step = (size_t)A.H * NP;
+  for (int c0 = 0; c0 < pieces; c0 += 8) {                 // eight pieces' loads in flight, then their chain
+    float own[8], dec[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      const bool in = c0 + i < pieces;
+      own[i] = in ? ps[(size_t)(c0 + i) * step] : 0.f;
+      dec[i] = in ? pd[(size_t)(c0 + i) * A.H] : 1.f;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      if (c0 + i < pieces) {
+        ps[(size_t)(c0 + i) * step] = carry;
+        carry = fmaf(dec[i], carry, own[i]);
+      }
+    }
   }
   *slot = carry;
 }
@@ -309,13 +355,15 @@ HB_EXPORT int hb_ssd_scan(const float* xbc, long ldx, const float* dt, long lddt
   A.vec4 = !((N | P) & 3) && !(ldx & 3) && !((uintptr_t)xbc & 15);
   A.piece_state = piece_state; A.piece_decay = piece_decay; A.L = piece_len; A.pieces = pieces;
   const int threads = ((P * ks + 31) / 32) * 32;
-  const int RW = ((2 * N + P + 1 + 3) / 4) * 4;
+  const bool fast = A.vec4 && N == per * ks && (per == 8 || per == 16 || per == 32 || per == 64);
+  const int NQ = fast ? N + 4 * ks : N;
+  const int RW = ((2 * NQ + P + 1 + 3) / 4) * 4;
   const size_t smem = (size_t)2 * SS_CH * RW * sizeof(float);
   if (smem > 200 * 1024) HB_FAIL("hb_ssd_scan: heads of %d x %d do not fit shared memory", N, P);
   if (n_requests > 65535) HB_FAIL("hb_ssd_scan: the grid is too large");
 #define SS_LAUNCH_MODE(DPT, MODE, GRID)                                                                            \
   HB_DISPATCH_1(w_dt, "hb_ssd_scan", do {                                                                          \
-    auto kern = ssd_scan_kernel<DPT, TA, MODE>;                                                                    \
+    auto kern = fast ? ssd_scan_kernel<DPT, TA, MODE, true> : ssd_scan_kernel<DPT, TA, MODE, false>;               \
     if (smem + 4096 > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
     hb_launch(kern, GRID, dim3(threads), smem, s, A);                                                              \
   } while (0))
