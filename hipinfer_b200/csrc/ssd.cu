@@ -118,10 +118,18 @@ struct SsdArgs {
   const int* q_start; const int* q_len; const int* slot;
   float* y;                              // [T][H P]
   int H, P, N, G, KS, vec4;
-  float* piece_state;                    // pieces only: [requests][pieces][H][N][P]
-  float* piece_decay;                    // pieces only: [requests][pieces][H]
+  float* piece_state;                    // pieces only: [all requests' pieces, request after request][H][N][P]
+  float* piece_decay;                    // pieces only: [all requests' pieces][H]
   int L, pieces;                         // tokens a piece, most pieces a request
 };
+
+// The first piece of request r among all requests' pieces: requests lie one after another, each with as many pieces as
+// its rows need, so a step of one long portion beside many single tokens holds few pieces.
+__device__ __forceinline__ int ss_piece_base(const int* __restrict__ q_len, int r, int L) {
+  int base = 0;
+  for (int i = 0; i < r; i++) base += (q_len[i] + L - 1) / L;
+  return base;
+}
 
 // MODE of the walk: whole portions from and into the state slot; a piece from zero (no y; leaves its state and the product
 // of its decays); a piece from its starting state (y only).
@@ -155,7 +163,7 @@ __global__ void __launch_bounds__(SsdThreads<DPT>::MAX, 1) ssd_scan_kernel(SsdAr
   const int len = MODE == SS_WHOLE ? A.q_len[r] : min(A.q_len[r], j_begin + A.L);      // the walk ends here
   if (MODE != SS_WHOLE && j_begin >= len) return;
   float* S_g = MODE == SS_WHOLE ? A.state + ((size_t)A.slot[r] * H + h) * N * P
-                                : A.piece_state + (((size_t)r * A.pieces + blockIdx.z) * H + h) * N * P;
+                                : A.piece_state + (((size_t)ss_piece_base(A.q_len, r, A.L) + blockIdx.z) * H + h) * N * P;
   // a token's row in shared memory: [B -> dt B (NQ) | C (NQ) | x (P) | dt_raw -> decay (1) | pad], two chunks deep
   const int NQ = FAST ? N + 4 * KS : N;
   const int RW = ((2 * NQ + P + 1 + 3) / 4) * 4;
@@ -290,7 +298,8 @@ __global__ void __launch_bounds__(SsdThreads<DPT>::MAX, 1) ssd_scan_kernel(SsdAr
     const int n = FAST ? ks * DPT + i : i * KS + ks;
     if (live && n < N) S_g[(size_t)n * P + p] = S[i];
   }
-  if (MODE == SS_PIECE_LOCAL && tid == 0) A.piece_decay[((size_t)r * A.pieces + blockIdx.z) * H + h] = decays;
+  if (MODE == SS_PIECE_LOCAL && tid == 0)
+    A.piece_decay[((size_t)ss_piece_base(A.q_len, r, A.L) + blockIdx.z) * H + h] = decays;
 }
 
 // The pieces' starting states, one after another: an element of (request, head) walks its pieces, leaves in each the state
@@ -306,8 +315,9 @@ __global__ void __launch_bounds__(256) ssd_carry_kernel(SsdArgs A) {
   const int pieces = (len + A.L - 1) / A.L;
   float* slot = A.state + (size_t)A.slot[r] * A.H * NP + e;
   float carry = *slot;
-  float* ps = A.piece_state + (size_t)r * A.pieces * A.H * NP + e;
-  const float* pd = A.piece_decay + (size_t)r * A.pieces * A.H + h;
+  const size_t base = (size_t)ss_piece_base(A.q_len, r, A.L);
+  float* ps = A.piece_state + base * A.H * NP + e;
+  const float* pd = A.piece_decay + base * A.H + h;
   const size_t step = (size_t)A.H * NP;
   for (int c0 = 0; c0 < pieces; c0 += 8) {                 // eight pieces' loads in flight, then their chain
     float own[8], dec[8];
@@ -332,8 +342,8 @@ HB_EXPORT int hb_ssd_scan(const float* xbc, long ldx, const float* dt, long lddt
                           const void* d_skip, int w_dt, float* state, const int* q_start, const int* q_len, const int* slot,
                           float* y, int n_requests, int H, int P, int N, int G, int piece_len, int pieces, float* piece_state,
                           float* piece_decay, cudaStream_t s) {
-  // pieces > 0: the three-launch form over pieces of piece_len tokens, with room for `pieces` pieces a request in
-  // piece_state [n_requests][pieces][H][N][P] and piece_decay [n_requests][pieces][H]
+  // pieces > 0: the three-launch form over pieces of piece_len tokens, no request with more than `pieces` of them, with
+  // room for all requests' pieces (at most rows / piece_len + n_requests) in piece_state [.][H][N][P] and piece_decay [.][H]
   if (n_requests <= 0) return 0;
   if (pieces > 0 && (piece_len <= 0 || !piece_state || !piece_decay || pieces > 65535)) HB_FAIL("hb_ssd_scan: %d pieces of %d", pieces, piece_len);
   if (P > 1024 || G <= 0 || H % G) HB_FAIL("hb_ssd_scan: %d heads of %d in %d groups", H, P, G);

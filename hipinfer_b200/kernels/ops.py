@@ -1123,8 +1123,9 @@ def ssd_scan(xbc: torch.Tensor, dt: torch.Tensor, dt_bias: torch.Tensor, a_log: 
     L, pieces, piece_state, piece_decay = int(SSD_PIECE_TOKENS), 0, None, None
     if L > 0 and batch.max_q_len >= 3 * L:
         pieces = -(-batch.max_q_len // L)
-        piece_state = torch.empty(batch.n_requests, pieces, heads, n_state, vdim, dtype=torch.float32, device=xbc.device)
-        piece_decay = torch.empty(batch.n_requests, pieces, heads, dtype=torch.float32, device=xbc.device)
+        room = T // L + batch.n_requests               # all requests' pieces: every request ends with at most one short piece
+        piece_state = torch.empty(room, heads, n_state, vdim, dtype=torch.float32, device=xbc.device)
+        piece_decay = torch.empty(room, heads, dtype=torch.float32, device=xbc.device)
     _call("hybrid", "hb_ssd_scan", xbc.data_ptr(), xbc.stride(0), dt.data_ptr(), dt.stride(0), dt_bias.data_ptr(),
           a_log.data_ptr(), d_skip.data_ptr(), _dt(dt_bias), state.data_ptr(), batch.req_q_start.data_ptr(),
           batch.req_q_len.data_ptr(), batch.req_state_slot.data_ptr(), y.data_ptr(), batch.n_requests, heads, vdim, n_state,
