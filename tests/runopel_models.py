@@ -54,7 +54,7 @@ B = model(97, 48, [latent(3, 8, 8, 8, 24, window=1, mlp=moe(40, 1, 1)), ssm(3, 1
           streams=1, mult=1.0, logit_scale=1.0, eps=1e-6, max_positions=600)
 # C: wider, no streams at all (the plain residual); windows that cross pages and key tiles (70, 200); heads of 64 x 128
 #    and 32 x 64; sixteen experts of which four
-C = model(211, 128, [ssm(2, 64, 128, mlp=moe(64, 16, 4)), latent(8, 32, 16, 32, 64, window=70, mlp=dense(192, limit=7.0)),
+C = model(211, 128, [ssm(2, 64, 128, mlp=moe(64, 16, 4)), latent(8, 48, 16, 32, 96, window=70, mlp=dense(208, limit=7.0)),
                      ssm(8, 32, 64, groups=2, norm_groups=4, conv=3), latent(4, 64, 32, 48, 96, window=200, mlp=moe(96, 4, 2))],
           mult=0.5, logit_scale=2.0, max_positions=900)
 # D: sizes no vectorised kernel takes: a width that is no multiple of 4, heads of 10 and 6 and 7, a latent of 20, four streams

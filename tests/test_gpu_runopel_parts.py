@@ -45,7 +45,7 @@ def batch_of(lengths, ctx=None, slots=None):
 
 # ------------------------------------------------------------------------------------------ residual streams
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("S,W", [(1, 50), (2, 192), (3, 64), (8, 1000), (1, 128), (2, 2048), (4, 4096), (2, 4100)])
+@pytest.mark.parametrize("S,W", [(1, 50), (2, 176), (3, 64), (8, 1000), (1, 128), (2, 2048), (4, 4096), (2, 4100)])
 def test_streams_read_norm_and_write_back(dtype, S, W):
     from hipinfer_b200.kernels import ops
 
@@ -128,7 +128,7 @@ def test_causal_convolution_carries_its_last_inputs(dtype, C, K):
         close(torch.cat(got[r]), want[r], torch.float32, f"request {r}")
 
 
-@pytest.mark.parametrize("H,P,N,G", [(4, 16, 8, 2), (3, 6, 7, 1), (2, 64, 128, 1), (6, 48, 48, 3), (1, 128, 16, 1), (2, 10, 5, 2)])
+@pytest.mark.parametrize("H,P,N,G", [(4, 16, 8, 2), (3, 6, 7, 1), (2, 64, 128, 1), (6, 40, 56, 3), (1, 128, 16, 1), (2, 10, 5, 2)])
 def test_recurrence_against_the_plain_scan(H, P, N, G, monkeypatch):
     """Whole, in portions and token by token, each request in one walk: the same bits (a token's arithmetic does not depend
     on where a portion starts), and the plain scan's values. Head 0 hardly decays and token 0 is huge: it is still there
@@ -163,7 +163,7 @@ def test_recurrence_against_the_plain_scan(H, P, N, G, monkeypatch):
 
 
 @pytest.mark.parametrize("piece", [4, 16, 64])
-@pytest.mark.parametrize("H,P,N,G", [(4, 16, 8, 2), (3, 6, 7, 1), (2, 64, 128, 1), (6, 48, 48, 3)])
+@pytest.mark.parametrize("H,P,N,G", [(4, 16, 8, 2), (3, 6, 7, 1), (2, 64, 128, 1), (6, 40, 56, 3)])
 def test_recurrence_in_pieces(H, P, N, G, piece, monkeypatch):
     """Long portions in pieces (each from zero, the starting states one after another, each again for y): three requests of
     unequal length in one step, one of a single token, one that ends in the middle of a piece, each after a first portion
@@ -254,7 +254,7 @@ def _routed(dtype, W, F, E, top, seed=0):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("W,F,E,top,T", [(64, 32, 5, 2, 9), (50, 22, 3, 3, 7), (128, 96, 16, 4, 200), (192, 96, 8, 1, 130), (48, 40, 1, 1, 5),
+@pytest.mark.parametrize("W,F,E,top,T", [(64, 32, 5, 2, 9), (50, 22, 3, 3, 7), (128, 96, 16, 4, 200), (160, 64, 6, 1, 130), (48, 40, 1, 1, 5),
                                          (2200, 24, 3, 2, 19), (4360, 16, 2, 1, 11), (2112, 72, 4, 2, 40), (96, 160, 3, 2, 30)])
 def test_routed_feed_forward_row_by_row_grouped_and_sorted(dtype, W, F, E, top, T, monkeypatch):
     """The scores multiply the experts' inputs and are not renormalised; single rows one by one (no sorting), single rows
@@ -304,7 +304,7 @@ def _plain_window_rows(q, keys, values, positions, scale, window):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,R,Dr,window,ps", [(8, 64, 16, 72, 16), (3, 40, 8, 24, 16), (2, 20, 6, 5, 8), (4, 32, 32, 1, 16), (4, 96, 32, 200, 16)])
+@pytest.mark.parametrize("H,R,Dr,window,ps", [(6, 48, 16, 70, 16), (3, 40, 8, 24, 16), (2, 20, 6, 5, 8), (4, 32, 32, 1, 16), (4, 96, 32, 200, 16)])
 def test_single_rows_in_the_latent_s_space_see_exactly_the_window(dtype, H, R, Dr, window, ps):
     """Rows of two requests over one plane of [latent | rotated key part] rows, the values its first columns. The key just
     inside the window has a large score and the key just outside a larger one: one position off in either direction and
@@ -344,7 +344,7 @@ def test_single_rows_in_the_latent_s_space_see_exactly_the_window(dtype, H, R, D
     close(out.view(len(rows), H, R), want, dtype, "rows")
 
 
-@pytest.mark.parametrize("H,D,E,window,ctx,n", [(8, 48, 32, 72, 300, 130), (2, 32, 32, 24, 0, 100), (4, 64, 64, 1, 40, 64), (3, 96, 64, 200, 500, 17)])
+@pytest.mark.parametrize("H,D,E,window,ctx,n", [(6, 64, 32, 70, 300, 130), (2, 32, 32, 24, 0, 100), (4, 64, 64, 1, 40, 64), (3, 96, 64, 200, 500, 17)])
 def test_a_portion_s_rows_see_exactly_the_window(H, D, E, window, ctx, n):
     """The tensor-core kernel over keys and values made from the first kept page on: rows [first, ctx + n) only."""
     from hipinfer_b200.kernels import ops
