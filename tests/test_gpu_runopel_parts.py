@@ -81,7 +81,7 @@ def test_streams_read_norm_and_write_back(dtype, S, W):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("I,group", [(64, 16), (56, 56), (7, 7)])
+@pytest.mark.parametrize("I,group", [(64, 16), (56, 56), (7, 7), (4096, 16), (30, 6)])
 def test_gate_with_biases_and_limits(dtype, I, group):
     from hipinfer_b200.kernels import ops
 
