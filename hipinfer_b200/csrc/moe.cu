@@ -477,9 +477,35 @@ __global__ void __launch_bounds__(256) moe_act_kernel(const float* __restrict__ 
   }
 }
 
+// Four columns a thread (F a multiple of four, aligned rows): the same values.
+template <typename TO>
+__global__ void __launch_bounds__(256) moe_act_vec_kernel(const float* __restrict__ gu, const int* __restrict__ src,
+                                                          const float* __restrict__ weight, TO* __restrict__ act, long n4, int F) {
+  hb_pdl_launch();
+  hb_pdl_wait();
+  const int F4 = F >> 2;
+  for (long idx = (long)blockIdx.x * 256 + threadIdx.x; idx < n4; idx += (long)gridDim.x * 256) {
+    const long r = idx / F4;
+    const int j = (int)(idx - r * F4) << 2;
+    const float s = weight[src[r]];
+    const float4 gv = *(const float4*)(gu + r * 2 * F + j), uv = *(const float4*)(gu + r * 2 * F + F + j);
+    const float g0 = s * gv.x, g1 = s * gv.y, g2 = s * gv.z, g3 = s * gv.w;
+    hb_store4(act + r * F + j, make_float4(g0 / (1.f + expf(-g0)) * (s * uv.x), g1 / (1.f + expf(-g1)) * (s * uv.y),
+                                           g2 / (1.f + expf(-g2)) * (s * uv.z), g3 / (1.f + expf(-g3)) * (s * uv.w)));
+  }
+}
+
 HB_EXPORT int hb_moe_act(const float* gu, const int* src, const float* weight, void* act, int o_dt, int pairs, int F,
                          cudaStream_t s) {
   if (pairs <= 0) return 0;
+  if (F % 4 == 0 && !(((uintptr_t)gu | (uintptr_t)act) & 15)) {
+    const long n4 = (long)pairs * (F / 4);
+    const int blocks4 = (int)((n4 + 255) / 256 < 148 * 16 ? (n4 + 255) / 256 : 148 * 16);
+    HB_DISPATCH_1(o_dt, "hb_moe_act",
+                  (hb_launch(moe_act_vec_kernel<TA>, dim3(blocks4), dim3(256), 0, s, gu, src, weight, (TA*)act, n4, F)));
+    HB_CHECK_LAUNCH("hb_moe_act");
+    return 0;
+  }
   const long n = (long)pairs * F;
   const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
   HB_DISPATCH_1(o_dt, "hb_moe_act", (hb_launch(moe_act_kernel<TA>, dim3(blocks), dim3(256), 0, s, gu, src, weight, (TA*)act, n, F)));
