@@ -475,20 +475,21 @@ HB_EXPORT int hb_swiglu(const void* gu, int gu_dt, long ld_gu, void* act, int ac
 // Rotary table: (cos, sin) of angle = float(p) * inv_freq[i], the angle a 32-bit product, the
 // functions evaluated in double (src/api.cu:1430-1441), kept in 32-bit.
 // ---------------------------------------------------------------------------------------
-__global__ void rope_table_kernel(const float* __restrict__ inv_freq, float2* __restrict__ table, int n_pos, int half) {
+__global__ void rope_table_kernel(const float* __restrict__ inv_freq, float2* __restrict__ table, int n_pos, int half, double mag) {
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= n_pos * half) return;
   const int p = idx / half, i = idx - p * half;
   const float angle = __fmul_rn((float)p, inv_freq[i]);
   double sn, cs;
   sincos((double)angle, &sn, &cs);
-  table[idx] = make_float2((float)cs, (float)sn);
+  table[idx] = make_float2((float)(cs * mag), (float)(sn * mag));
 }
 
-HB_EXPORT int hb_rope_table(const float* inv_freq, void* table, int n_pos, int half, cudaStream_t s) {
+// mag multiplies both cos and sin (1: a plain rotation).
+HB_EXPORT int hb_rope_table(const float* inv_freq, void* table, int n_pos, int half, double mag, cudaStream_t s) {
   if (n_pos <= 0 || half <= 0) return 0;
   const long n = (long)n_pos * half;
-  rope_table_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(inv_freq, (float2*)table, n_pos, half);
+  rope_table_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(inv_freq, (float2*)table, n_pos, half, mag);
   HB_CHECK_LAUNCH("hb_rope_table");
   return 0;
 }
@@ -600,17 +601,20 @@ HB_EXPORT int hb_rope_kv(const void* qkv, int qkv_dt, long ld, const int* pos, c
 // rotated by the row's position (pairs (i, i + rot/2) with pairing 0, (2i, 2i + 1) with pairing 1; the rest passes); then, if
 // asked, the head is divided by its root mean square over D (eps inside the root). q goes to q_out [T][H * D], k and v
 // to the token's page slot (planes [page][G][page_size][D] and [...][E]). All of it is 32-bit and rounded once.
+// With pre_wq / pre_wk the q row (all H heads at once) and the k row are first divided by their own root mean square
+// (pre_eps inside the root) and multiplied by a weight per column, before the rotation.
 // No slot map (a layer that reads another layer's cache): q alone. A warp works on a head at a time.
 // ---------------------------------------------------------------------------------------
-template <typename TQ>
+template <typename TQ, typename TW>
 __global__ void __launch_bounds__(256) rope_norm_store_kernel(const float* __restrict__ proj, long ld, int q_off, int k_off,
                                                               int v_off, const int* __restrict__ pos,
                                                               const int* __restrict__ slot_map,
                                                               const float2* __restrict__ table, int rot, int rot_off,
                                                               int pairing, int unit_norm, float eps, TQ* __restrict__ q_out,
                                                               TQ* __restrict__ kc, TQ* __restrict__ vc, int H, int G, int D,
-                                                              int E, int page_size) {
-  extern __shared__ float rn_sh[];      // [8 warps][D]
+                                                              int E, int page_size, const TW* __restrict__ pre_wq,
+                                                              const TW* __restrict__ pre_wk, float pre_eps) {
+  extern __shared__ float rn_sh[];      // [8 warps][D], then 32 floats for the sums of a row norm
   hb_pdl_launch();
   hb_pdl_wait();
   const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, half = rot >> 1;
@@ -620,9 +624,27 @@ __global__ void __launch_bounds__(256) rope_norm_store_kernel(const float* __res
   const size_t page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot % page_size : 0;
   float* buf = rn_sh + warp * D;
   const int n_heads = H + (slot >= 0 ? G : 0);
+  // a norm over the WHOLE q row and the whole k row (all heads at once), with a weight per column, before the rotation
+  float fq = 1.f, fk = 1.f;
+  if (pre_wq) {
+    float* red = rn_sh + 8 * D;
+    float sq = 0.f, sk = 0.f;
+    for (int i = threadIdx.x; i < H * D; i += 256) sq = fmaf(row[q_off + i], row[q_off + i], sq);
+    fq = rsqrtf(hb_block_sum(sq, red) / (float)(H * D) + pre_eps);
+    if (slot >= 0) {
+      for (int i = threadIdx.x; i < G * D; i += 256) sk = fmaf(row[k_off + i], row[k_off + i], sk);
+      fk = rsqrtf(hb_block_sum(sk, red) / (float)(G * D) + pre_eps);
+    }
+  }
   for (int hh = warp; hh < n_heads; hh += 8) {
     const float* src = hh < H ? row + q_off + (size_t)hh * D : row + k_off + (size_t)(hh - H) * D;
-    for (int d = lane; d < D; d += 32) buf[d] = src[d];
+    if (pre_wq) {
+      const TW* pw = hh < H ? pre_wq + (size_t)hh * D : pre_wk + (size_t)(hh - H) * D;
+      const float pf = hh < H ? fq : fk;
+      for (int d = lane; d < D; d += 32) buf[d] = src[d] * pf * hb_to_float(pw[d]);
+    } else {
+      for (int d = lane; d < D; d += 32) buf[d] = src[d];
+    }
     __syncwarp();
     float ss = 0.f;
     for (int i = lane; i < half; i += 32) {
@@ -653,16 +675,18 @@ __global__ void __launch_bounds__(256) rope_norm_store_kernel(const float* __res
 HB_EXPORT int hb_rope_norm_store(const float* proj, long ld, int q_off, int k_off, int v_off, const int* pos,
                                  const int* slot_map, const void* table, int rot, int rot_off, int pairing, int unit_norm,
                                  float eps, void* q_out, void* kc, void* vc, int q_dt, int T, int H, int G, int D, int E, int page_size,
-                                 cudaStream_t s) {
+                                 const void* pre_wq, const void* pre_wk, int pre_dt, float pre_eps, cudaStream_t s) {
   if (T <= 0) return 0;
   if (rot < 0 || rot_off < 0 || rot_off + rot > D || (rot & 1)) HB_FAIL("hb_rope_norm_store: %d rotated dimensions from %d on of a head of %d", rot, rot_off, D);
   if (slot_map && (!kc || !vc || G <= 0 || E <= 0 || page_size <= 0)) HB_FAIL("hb_rope_norm_store: a slot map without caches or sizes");
-  const size_t smem = (size_t)8 * D * sizeof(float);
+  const size_t smem = (size_t)(8 * D + 32) * sizeof(float);
   if (smem > 48 * 1024) HB_FAIL("hb_rope_norm_store: heads of %d are too wide", D);
-  HB_DISPATCH_1(q_dt, "hb_rope_norm_store",
-                (hb_launch(rope_norm_store_kernel<TA>, T, 256, smem, s, proj, ld, q_off, k_off, v_off, pos, slot_map,
+  if ((pre_wq != nullptr) != (pre_wk != nullptr)) HB_FAIL("hb_rope_norm_store: a row norm needs the weights of q and of k");
+  if (!pre_wq) pre_dt = q_dt;
+  HB_DISPATCH_2(q_dt, pre_dt, "hb_rope_norm_store",
+                (hb_launch(rope_norm_store_kernel<TA, TB>, T, 256, smem, s, proj, ld, q_off, k_off, v_off, pos, slot_map,
                            (const float2*)table, rot, rot_off, pairing, unit_norm, eps, (TA*)q_out, (TA*)kc, (TA*)vc, H, G, D, E,
-                           page_size)));
+                           page_size, (const TB*)pre_wq, (const TB*)pre_wk, pre_eps)));
   HB_CHECK_LAUNCH("hb_rope_norm_store");
   return 0;
 }

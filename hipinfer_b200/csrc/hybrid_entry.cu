@@ -1,5 +1,6 @@
 // Error reporting of the `hybrid` library: residual streams with learned mixing (hyper-connections), the state-space
-// recurrence with a scalar decay per head and its short convolution, routed feed-forward layers, and a gated
+// recurrence with a scalar decay per head and its short convolution, the selective recurrence with a decay per (channel,
+// state) pair, the residual row after a sublayer with the norm after the sum, routed feed-forward layers, and a gated
 // activation with biases and limits.
 #include "common.cuh"
 

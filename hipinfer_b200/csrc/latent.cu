@@ -8,11 +8,12 @@
 // latent_prepare_kernel: from the 32-bit result of the first product (row = [.. cq_raw (Rq) .. c_raw (R) .. kr_raw (Dr) ..])
 //   cq = cq_raw / rms(cq_raw) * wq      -> cq_out [T][Rq]
 //   c  = c_raw / rms(c_raw) * wc        -> the token's cache row, columns [0, R)
-//   kr = rotated(kr_raw)                -> the token's cache row, columns [R, R + Dr)   (pairs (2i, 2i + 1), i < rot / 2)
+//   kr = rotated(kr_raw)                -> the token's cache row, columns [R, R + Dr)   (pairs (2i, 2i + 1), i < rot / 2,
+//                                          with pairing 1; pairs (i, i + rot / 2) with pairing 0)
 //   root mean squares with eps inside the root, all 32-bit, rounded once.
 // heads_linear_kernel: out[t, h, n] = sum_k a[t, h, k] Wt[h][k][n] (32-bit a, 32-bit sums), optionally times
-//   sigmoid(gate[t, h, n]); and, where asked, the `tail` columns after a's K are rotated the same way and copied behind
-//   out's N columns (the rotated part of a query).
+//   sigmoid(gate[t, h, n]) (or of one number per head, gate[t, h]); and, where asked, the `tail` columns after a's K are
+//   rotated the same way and copied behind out's N columns (the rotated part of a query).
 #include "common.cuh"
 
 template <typename TW, typename TO>
@@ -21,7 +22,7 @@ __global__ void __launch_bounds__(256) latent_prepare_kernel(const float* __rest
                                                              const int* __restrict__ pos, const int* __restrict__ slot_map,
                                                              const float2* __restrict__ table, int rot, float eps,
                                                              TO* __restrict__ cq_out, TO* __restrict__ cache, int Rq, int R,
-                                                             int Dr, int page_size) {
+                                                             int Dr, int page_size, int pairing) {
   __shared__ float sh[32];
   hb_pdl_launch();
   hb_pdl_wait();
@@ -41,24 +42,25 @@ __global__ void __launch_bounds__(256) latent_prepare_kernel(const float* __rest
   const int half = rot >> 1;
   const float2* cs = table + (size_t)pos[t] * half;
   for (int i = tid; i < half; i += 256) {
-    const float u = row[kr_off + 2 * i], v = row[kr_off + 2 * i + 1];
+    const int ia = pairing ? 2 * i : i, ib = pairing ? 2 * i + 1 : i + half;
+    const float u = row[kr_off + ia], v = row[kr_off + ib];
     const float2 c = cs[i];
-    dst[R + 2 * i] = hb_from_float<TO>(__fsub_rn(__fmul_rn(u, c.x), __fmul_rn(v, c.y)));
-    dst[R + 2 * i + 1] = hb_from_float<TO>(__fadd_rn(__fmul_rn(v, c.x), __fmul_rn(u, c.y)));
+    dst[R + ia] = hb_from_float<TO>(__fsub_rn(__fmul_rn(u, c.x), __fmul_rn(v, c.y)));
+    dst[R + ib] = hb_from_float<TO>(__fadd_rn(__fmul_rn(v, c.x), __fmul_rn(u, c.y)));
   }
   for (int i = rot + tid; i < Dr; i += 256) dst[R + i] = hb_from_float<TO>(row[kr_off + i]);
 }
 
 HB_EXPORT int hb_latent_prepare(const float* proj, long ld, int cq_off, int c_off, int kr_off, const void* wq, const void* wc,
                                 int w_dt, const int* pos, const int* slot_map, const void* table, int rot, float eps,
-                                void* cq_out, void* cache, int o_dt, int T, int Rq, int R, int Dr, int page_size,
+                                void* cq_out, void* cache, int o_dt, int T, int Rq, int R, int Dr, int page_size, int pairing,
                                 cudaStream_t s) {
   if (T <= 0) return 0;
   if (rot < 0 || rot > Dr || (rot & 1)) HB_FAIL("hb_latent_prepare: %d rotated dimensions of %d", rot, Dr);
   HB_DISPATCH_2(w_dt, o_dt, "hb_latent_prepare",
                 (hb_launch(latent_prepare_kernel<TA, TB>, T, 256, 0, s, proj, ld, cq_off, c_off, kr_off, (const TA*)wq,
                            (const TA*)wc, pos, slot_map, (const float2*)table, rot, eps, (TB*)cq_out, (TB*)cache, Rq, R, Dr,
-                           page_size)));
+                           page_size, pairing)));
   HB_CHECK_LAUNCH("hb_latent_prepare");
   return 0;
 }
@@ -76,7 +78,8 @@ __global__ void __launch_bounds__(HL_THREADS) heads_linear_kernel(const float* _
                                                                   int tail, int rot, const int* __restrict__ pos,
                                                                   const float2* __restrict__ table,
                                                                   const int* __restrict__ row_req,
-                                                                  const int* __restrict__ q_len, int row_limit) {
+                                                                  const int* __restrict__ q_len, int row_limit, int pairing,
+                                                                  int gate_per_head) {
   extern __shared__ float hl_a[];      // [HL_TM][K + tail], then [HL_KZ][HL_TM][HL_TN] partial sums
   hb_pdl_launch();
   hb_pdl_wait();
@@ -116,7 +119,7 @@ __global__ void __launch_bounds__(HL_THREADS) heads_linear_kernel(const float* _
       float o = 0.f;
 #pragma unroll
       for (int z = 0; z < HL_KZ; z++) o += red[(z * HL_TM + r) * HL_TN + nl];
-      if (gate) o *= 1.f / (1.f + expf(-gate[(size_t)(t0 + r) * ld_gate + gate_off + (size_t)h * N + n]));
+      if (gate) o *= 1.f / (1.f + expf(-gate[(size_t)(t0 + r) * ld_gate + gate_off + (gate_per_head ? (size_t)h : (size_t)h * N + n)]));
       out[(size_t)(t0 + r) * ldo + (size_t)h * o_head + n] = hb_from_float<TO>(o);
     }
   } else if (n < N + tail && kz == 0) {
@@ -126,10 +129,11 @@ __global__ void __launch_bounds__(HL_THREADS) heads_linear_kernel(const float* _
       const float* src = hl_a + r * KT_ + K;
       float y = src[j];
       if (j < rot) {
-        const int i = j >> 1;
+        const int i = pairing ? j >> 1 : (j < half ? j : j - half);
+        const bool second = pairing ? (j & 1) : (j >= half);
         const float2 c = table[(size_t)pos[t0 + r] * half + i];
-        const float u = src[2 * i], v = src[2 * i + 1];
-        y = (j & 1) ? __fadd_rn(__fmul_rn(v, c.x), __fmul_rn(u, c.y)) : __fsub_rn(__fmul_rn(u, c.x), __fmul_rn(v, c.y));
+        const float u = src[pairing ? 2 * i : i], v = src[pairing ? 2 * i + 1 : i + half];
+        y = second ? __fadd_rn(__fmul_rn(v, c.x), __fmul_rn(u, c.y)) : __fsub_rn(__fmul_rn(u, c.x), __fmul_rn(v, c.y));
       }
       out[(size_t)(t0 + r) * ldo + (size_t)h * o_head + n] = hb_from_float<TO>(y);
     }
@@ -141,7 +145,7 @@ __global__ void __launch_bounds__(HL_THREADS) heads_linear_kernel(const float* _
 HB_EXPORT int hb_heads_linear(const float* a, long lda, long a_head, const void* wt, int w_dt, void* out, int o_dt, long ldo,
                               long o_head, int T, int H, int K, int N, const float* gate, long ld_gate, int gate_off, int tail,
                               int rot, const int* pos, const void* table, const int* row_req, const int* q_len, int row_limit,
-                              cudaStream_t s) {
+                              int pairing, int gate_per_head, cudaStream_t s) {
   if (T <= 0 || H <= 0) return 0;
   if (tail && (!pos || !table || rot > tail || (rot & 1))) HB_FAIL("hb_heads_linear: a rotated tail needs positions and a table");
   const size_t smem = ((size_t)HL_TM * (K + tail) + (size_t)HL_KZ * HL_TM * HL_TN) * sizeof(float);
@@ -153,7 +157,8 @@ HB_EXPORT int hb_heads_linear(const float* a, long lda, long a_head, const void*
     auto kern = heads_linear_kernel<TW, TO>;                                                                    \
     if (smem + 4096 > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
     hb_launch(kern, grid, dim3(HL_THREADS), smem, s, a, lda, a_head, (const TW*)wt, (TO*)out, ldo, o_head, T, K, N, gate,  \
-              ld_gate, gate_off, tail, rot, pos, (const float2*)table, row_req, q_len, row_limit);              \
+              ld_gate, gate_off, tail, rot, pos, (const float2*)table, row_req, q_len, row_limit, pairing,     \
+              gate_per_head);                                                                                   \
   } while (0)
   HB_DISPATCH_2(w_dt, o_dt, "hb_heads_linear", HL_LAUNCH(TA, TB));
 #undef HL_LAUNCH

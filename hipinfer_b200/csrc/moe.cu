@@ -3,6 +3,9 @@
 //     out = sum over the chosen e of Wd_e (silu(Wg_e v) * (Wu_e v)),  v = s_e h
 // The score multiplies the expert's INPUT. Experts have no biases, so Wg_e (s h) = s (Wg_e h): the products run on h and
 // the score enters the activation in 32-bit, silu(s g) * (s u).
+// A second form (route mode 1, `at_output`): z = Wr h + b; the `top` largest LOGITS choose; the weights are the softmax over
+// the chosen logits alone and multiply the expert's RESULT, which, the down product being linear, is the activation times
+// the weight, silu(g) * u * s, again in 32-bit.
 //
 // moe_route_kernel          scores and the chosen experts of every row: expert [T][top], weight [T][top]
 // Few rows (decoding): no sorting, nothing on the host
@@ -25,8 +28,8 @@ constexpr int MR_THREADS = 128;
 
 template <typename TA, typename TW>
 __global__ void __launch_bounds__(MR_THREADS) moe_route_kernel(const TA* __restrict__ xn, long ldx, const TW* __restrict__ router,
-                                                               int* __restrict__ expert, float* __restrict__ weight, int W,
-                                                               int E, int top) {
+                                                               const TW* __restrict__ bias, int* __restrict__ expert,
+                                                               float* __restrict__ weight, int W, int E, int top, int mode) {
   extern __shared__ float mr_sm[];     // [W] the row, [E] the scores
   float* row = mr_sm;
   float* sc = mr_sm + W;
@@ -40,27 +43,44 @@ __global__ void __launch_bounds__(MR_THREADS) moe_route_kernel(const TA* __restr
     float acc = 0.f;
     for (int i = lane; i < W; i += 32) acc = fmaf(row[i], hb_to_float(wr[i]), acc);
     acc = hb_warp_sum(acc);
-    if (lane == 0) sc[e] = 1.f / (1.f + expf(-acc));
+    if (bias) acc += hb_to_float(bias[e]);
+    if (lane == 0) sc[e] = mode == 0 ? 1.f / (1.f + expf(-acc)) : acc;
   }
   __syncthreads();
   if (threadIdx.x == 0) {
+    float first = 0.f, den = 0.f;
     for (int k = 0; k < top; k++) {
-      int best = 0;
-      float bs = -2.f;
-      for (int e = 0; e < E; e++)
-        if (sc[e] > bs) {
-          bs = sc[e];
+      int best = -1;
+      float bs = 0.f;
+      for (int e = 0; e < E; e++) {
+        const float v = sc[e];
+        if (v != v) continue;          // NaN marks an expert that is taken
+        if (best < 0 || v > bs) {
+          bs = v;
           best = e;
         }
+      }
+      if (best < 0) best = 0;          // every score NaN (bad weights or input): stay inside the tables
       expert[(size_t)t * top + k] = best;
-      weight[(size_t)t * top + k] = bs;
-      sc[best] = -1.f;                 // scores lie in [0, 1]: a taken expert is never the largest again
+      if (mode == 0) weight[(size_t)t * top + k] = bs;
+      else {
+        // softmax over the chosen logits alone: the first chosen one is the largest
+        if (k == 0) first = bs;
+        const float ex = expf(bs - first);
+        weight[(size_t)t * top + k] = ex;
+        den += ex;
+      }
+      sc[best] = __int_as_float(0x7fc00000);
     }
+    if (mode != 0)
+      for (int k = 0; k < top; k++) weight[(size_t)t * top + k] /= den;
   }
 }
 
-HB_EXPORT int hb_moe_route(const void* xn, int x_dt, long ldx, const void* router, int w_dt, int* expert, float* weight, int T,
-                           int W, int E, int top, cudaStream_t s) {
+// mode 0: the scores are sigmoid(z) and the chosen scores are the weights; mode 1: the largest logits z choose and the
+// weights are the softmax over the chosen logits alone. bias (the router's element type, or null) is added to z.
+HB_EXPORT int hb_moe_route(const void* xn, int x_dt, long ldx, const void* router, const void* bias, int w_dt, int* expert,
+                           float* weight, int T, int W, int E, int top, int mode, cudaStream_t s) {
   if (T <= 0) return 0;
   if (top < 1 || top > E) HB_FAIL("hb_moe_route: top %d of %d experts", top, E);
   const size_t smem = (size_t)(W + E) * sizeof(float);
@@ -68,7 +88,8 @@ HB_EXPORT int hb_moe_route(const void* xn, int x_dt, long ldx, const void* route
   HB_DISPATCH_2(x_dt, w_dt, "hb_moe_route", do {
     auto kern = moe_route_kernel<TA, TB>;
     if (smem > 40 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    hb_launch(kern, dim3(T), dim3(MR_THREADS), smem, s, (const TA*)xn, ldx, (const TB*)router, expert, weight, W, E, top);
+    hb_launch(kern, dim3(T), dim3(MR_THREADS), smem, s, (const TA*)xn, ldx, (const TB*)router, (const TB*)bias, expert, weight,
+              W, E, top, mode);
   } while (0));
   HB_CHECK_LAUNCH("hb_moe_route");
   return 0;
@@ -100,7 +121,7 @@ template <typename TA, typename TW, typename TO>
 __global__ void __launch_bounds__(MG_THREADS) moe_gate_up_rows_kernel(const TA* __restrict__ xn, long ldx,
                                                                       const TW* __restrict__ wgu, const int* __restrict__ expert,
                                                                       const float* __restrict__ weight, TO* __restrict__ act,
-                                                                      int W, int F, int top, int vec) {
+                                                                      int W, int F, int top, int vec, int at_output) {
   extern __shared__ __align__(16) float mg_row[];      // [W]
   hb_pdl_launch();
   hb_pdl_wait();
@@ -108,18 +129,19 @@ __global__ void __launch_bounds__(MG_THREADS) moe_gate_up_rows_kernel(const TA* 
   for (int i = threadIdx.x; i < W; i += MG_THREADS) mg_row[i] = hb_to_float(xn[(size_t)t * ldx + i]);
   __syncthreads();
   const int e = expert[pair];
-  const float s = weight[pair];
+  const float sw = weight[pair];
+  const float s = at_output ? 1.f : sw, so = at_output ? sw : 1.f;     // the weight multiplies the input, or the result
   const TW* we = wgu + (size_t)e * 2 * F * W;          // [gate rows (F) | up rows (F)][W]
   const int j1 = min(F, (int)(blockIdx.x + 1) * MG_ROWS);
   for (int j = blockIdx.x * MG_ROWS + warp; j < j1; j += MG_THREADS / 32) {
     const float g = s * moe_warp_dot(we + (size_t)j * W, mg_row, W, lane, vec);
     const float u = s * moe_warp_dot(we + (size_t)(F + j) * W, mg_row, W, lane, vec);
-    if (lane == 0) act[(size_t)pair * F + j] = hb_from_float<TO>(g / (1.f + expf(-g)) * u);
+    if (lane == 0) act[(size_t)pair * F + j] = hb_from_float<TO>(g / (1.f + expf(-g)) * u * so);
   }
 }
 
 HB_EXPORT int hb_moe_gate_up_rows(const void* xn, int x_dt, long ldx, const void* wgu, int w_dt, const int* expert,
-                                  const float* weight, void* act, int T, int W, int F, int top, cudaStream_t s) {
+                                  const float* weight, void* act, int T, int W, int F, int top, int at_output, cudaStream_t s) {
   if (T <= 0) return 0;
   const size_t smem = (size_t)W * sizeof(float);
   if (smem > 200 * 1024) HB_FAIL("hb_moe_gate_up_rows: a row of %d does not fit shared memory", W);
@@ -130,7 +152,7 @@ HB_EXPORT int hb_moe_gate_up_rows(const void* xn, int x_dt, long ldx, const void
   HB_DISPATCH_2(x_dt, w_dt, "hb_moe_gate_up_rows", do {
     auto kern = moe_gate_up_rows_kernel<TA, TB, TA>;
     if (smem > 40 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    hb_launch(kern, grid, dim3(MG_THREADS), smem, s, (const TA*)xn, ldx, (const TB*)wgu, expert, weight, (TA*)act, W, F, top, vec);
+    hb_launch(kern, grid, dim3(MG_THREADS), smem, s, (const TA*)xn, ldx, (const TB*)wgu, expert, weight, (TA*)act, W, F, top, vec, at_output);
   } while (0));
   HB_CHECK_LAUNCH("hb_moe_gate_up_rows");
   return 0;
@@ -465,50 +487,54 @@ HB_EXPORT int hb_moe_gather(const void* xn, int x_dt, long ldx, const int* src, 
 // gu [rows][g (F) | u (F)] 32-bit, sorted rows; the pair's score enters here
 template <typename TO>
 __global__ void __launch_bounds__(256) moe_act_kernel(const float* __restrict__ gu, const int* __restrict__ src,
-                                                      const float* __restrict__ weight, TO* __restrict__ act, long n, int F) {
+                                                      const float* __restrict__ weight, TO* __restrict__ act, long n, int F,
+                                                      int at_output) {
   hb_pdl_launch();
   hb_pdl_wait();
   for (long idx = (long)blockIdx.x * 256 + threadIdx.x; idx < n; idx += (long)gridDim.x * 256) {
     const long r = idx / F;
     const int j = (int)(idx - r * F);
-    const float s = weight[src[r]];
+    const float sw = weight[src[r]];
+    const float s = at_output ? 1.f : sw, so = at_output ? sw : 1.f;
     const float g = s * gu[r * 2 * F + j], u = s * gu[r * 2 * F + F + j];
-    act[idx] = hb_from_float<TO>(g / (1.f + expf(-g)) * u);
+    act[idx] = hb_from_float<TO>(g / (1.f + expf(-g)) * u * so);
   }
 }
 
 // Four columns a thread (F a multiple of four, aligned rows): the same values.
 template <typename TO>
 __global__ void __launch_bounds__(256) moe_act_vec_kernel(const float* __restrict__ gu, const int* __restrict__ src,
-                                                          const float* __restrict__ weight, TO* __restrict__ act, long n4, int F) {
+                                                          const float* __restrict__ weight, TO* __restrict__ act, long n4, int F,
+                                                          int at_output) {
   hb_pdl_launch();
   hb_pdl_wait();
   const int F4 = F >> 2;
   for (long idx = (long)blockIdx.x * 256 + threadIdx.x; idx < n4; idx += (long)gridDim.x * 256) {
     const long r = idx / F4;
     const int j = (int)(idx - r * F4) << 2;
-    const float s = weight[src[r]];
+    const float sw = weight[src[r]];
+    const float s = at_output ? 1.f : sw, so = at_output ? sw : 1.f;
     const float4 gv = *(const float4*)(gu + r * 2 * F + j), uv = *(const float4*)(gu + r * 2 * F + F + j);
     const float g0 = s * gv.x, g1 = s * gv.y, g2 = s * gv.z, g3 = s * gv.w;
-    hb_store4(act + r * F + j, make_float4(g0 / (1.f + expf(-g0)) * (s * uv.x), g1 / (1.f + expf(-g1)) * (s * uv.y),
-                                           g2 / (1.f + expf(-g2)) * (s * uv.z), g3 / (1.f + expf(-g3)) * (s * uv.w)));
+    hb_store4(act + r * F + j, make_float4(g0 / (1.f + expf(-g0)) * (s * uv.x) * so, g1 / (1.f + expf(-g1)) * (s * uv.y) * so,
+                                           g2 / (1.f + expf(-g2)) * (s * uv.z) * so, g3 / (1.f + expf(-g3)) * (s * uv.w) * so));
   }
 }
 
 HB_EXPORT int hb_moe_act(const float* gu, const int* src, const float* weight, void* act, int o_dt, int pairs, int F,
-                         cudaStream_t s) {
+                         int at_output, cudaStream_t s) {
   if (pairs <= 0) return 0;
   if (F % 4 == 0 && !(((uintptr_t)gu | (uintptr_t)act) & 15)) {
     const long n4 = (long)pairs * (F / 4);
     const int blocks4 = (int)((n4 + 255) / 256 < 148 * 16 ? (n4 + 255) / 256 : 148 * 16);
     HB_DISPATCH_1(o_dt, "hb_moe_act",
-                  (hb_launch(moe_act_vec_kernel<TA>, dim3(blocks4), dim3(256), 0, s, gu, src, weight, (TA*)act, n4, F)));
+                  (hb_launch(moe_act_vec_kernel<TA>, dim3(blocks4), dim3(256), 0, s, gu, src, weight, (TA*)act, n4, F, at_output)));
     HB_CHECK_LAUNCH("hb_moe_act");
     return 0;
   }
   const long n = (long)pairs * F;
   const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
-  HB_DISPATCH_1(o_dt, "hb_moe_act", (hb_launch(moe_act_kernel<TA>, dim3(blocks), dim3(256), 0, s, gu, src, weight, (TA*)act, n, F)));
+  HB_DISPATCH_1(o_dt, "hb_moe_act", (hb_launch(moe_act_kernel<TA>, dim3(blocks), dim3(256), 0, s, gu, src, weight, (TA*)act, n, F, at_output)));
   HB_CHECK_LAUNCH("hb_moe_act");
   return 0;
 }

@@ -1,0 +1,242 @@
+// The selective state-space recurrence with a decay per (channel, state) pair (the Mamba-1 form), and the sum that
+// joins two side-by-side mixers.
+//
+// Per token, for every channel c of `inner` and state n of N, with the step's 32-bit inputs x [T][inner] (after the short
+// convolution and silu), dt_raw [T][inner] (the step-size product without its bias), B and C [T][N] (shared by all
+// channels) and the gate's pre-activation z [T][inner]:
+//     dt = softplus(dt_raw + dt_bias_c);  A = -exp(A_log[c][n])
+//     S[c][n] <- exp(dt A) S[c][n] + (dt x_c) B_n;   y_c = sum_n S[c][n] C_n + D_c x_c;   out_c = y_c * silu(z_c)
+// The state S [inner][N] lives in 32-bit in the request's state slot and is carried from token to token and from step to
+// step; step sizes, decays, the exponentials and the sums are 32-bit (expf, log1pf; no fast-math), the result is rounded
+// once. A block owns (a tile of channels, a request) and walks the request's rows of the step in order: KS threads share a
+// channel, thread ks holds the states n = ks + i KS in registers, the KS partial sums of y are joined by shuffles. Tokens
+// go by in chunks of SEL_CH: a chunk's rows are asked for a chunk ahead (cp.async, two buffers), the step sizes are
+// finished in place, the chunk's results leave through shared memory in whole rows. Requests, lengths and state slots come
+// from device arrays, so a decode-only step replays from a CUDA graph; a token's arithmetic does not depend on where a
+// portion or a chunk starts.
+#include "common.cuh"
+
+constexpr int SEL_CH = 16;         // tokens a chunk
+constexpr int SEL_THREADS = 64;
+
+__device__ __forceinline__ void sel_cp4(float* dst, const float* src) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
+}
+__device__ __forceinline__ void sel_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void sel_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ float sel_softplus(float v) { return fmaxf(v, 0.f) + log1pf(expf(-fabsf(v))); }
+
+struct SelArgs {
+  const float* x; long ldx;          // [T][inner] after convolution and silu
+  const float* dt; long lddt;        // [T][inner] step-size product, no bias
+  const float* bc; long ldbc;        // a row holds B [N] then C [N]
+  const float* z; long ldz;          // [T][inner] gate pre-activation
+  const void* dt_bias; const void* a_log; const void* d_skip;   // [inner], [inner][N], [inner]
+  float* state;                      // [slots][inner][N]
+  const int* q_start; const int* q_len; const int* slot;
+  void* out; long ldo;               // [T][inner]
+  int inner, N, KS;
+};
+
+// shared memory of a block: two buffers of a chunk's rows, each [SEL_CH][2N + 3 CPB]: B | C | dt | x | z (z becomes the result)
+template <typename TW, typename TO, int NPT>
+__global__ void __launch_bounds__(SEL_THREADS) selective_scan_kernel(SelArgs A) {
+  extern __shared__ float sel_sm[];
+  hb_pdl_launch();
+  const int KS = A.KS, CPB = SEL_THREADS / KS, N = A.N;
+  const int cl = threadIdx.x / KS, ks = threadIdx.x % KS;
+  const int c0 = blockIdx.x * CPB, c = c0 + cl, r = blockIdx.y;
+  const bool live = c < A.inner;
+  const int nch = min(CPB, A.inner - c0);
+  const int row_w = 2 * N + 3 * CPB;
+  float* buf[2] = {sel_sm, sel_sm + SEL_CH * row_w};
+  // constants of the thread: its decays' rates, the skip weight and the bias (weights: before the wait)
+  float rate[NPT], S[NPT];
+  const TW* al = (const TW*)A.a_log;
+#pragma unroll
+  for (int i = 0; i < NPT; i++) {
+    const int n = ks + i * KS;
+    rate[i] = (live && n < N) ? -expf(hb_to_float(al[(size_t)c * N + n])) : 0.f;
+  }
+  const float dskip = live ? hb_to_float(((const TW*)A.d_skip)[c]) : 0.f;
+  hb_pdl_wait();
+  const int len = A.q_len[r], t0 = A.q_start[r];
+  if (len <= 0) return;
+  float* st = A.state + ((size_t)A.slot[r] * A.inner + (live ? c : 0)) * N;
+#pragma unroll
+  for (int i = 0; i < NPT; i++) {
+    const int n = ks + i * KS;
+    S[i] = (live && n < N) ? st[n] : 0.f;
+  }
+  auto fetch = [&](int j0, float* b) {
+    const int n = min(SEL_CH, len - j0);
+    for (int i = threadIdx.x; i < n * 2 * N; i += SEL_THREADS) {
+      const int j = i / (2 * N), k = i - j * 2 * N;
+      sel_cp4(b + j * row_w + k, A.bc + (size_t)(t0 + j0 + j) * A.ldbc + k);
+    }
+    for (int i = threadIdx.x; i < n * nch; i += SEL_THREADS) {
+      const int j = i / nch, k = i - j * nch;
+      const size_t t = (size_t)(t0 + j0 + j);
+      float* row = b + j * row_w + 2 * N;
+      sel_cp4(row + k, A.dt + t * A.lddt + c0 + k);
+      sel_cp4(row + CPB + k, A.x + t * A.ldx + c0 + k);
+      sel_cp4(row + 2 * CPB + k, A.z + t * A.ldz + c0 + k);
+    }
+    sel_commit();
+  };
+  fetch(0, buf[0]);
+  const TW* dtb = (const TW*)A.dt_bias;
+  int which = 0;
+  for (int j0 = 0; j0 < len; j0 += SEL_CH, which ^= 1) {
+    float* b = buf[which];
+    const int n_tok = min(SEL_CH, len - j0);
+    if (j0 + SEL_CH < len) {
+      fetch(j0 + SEL_CH, buf[which ^ 1]);
+      sel_wait<1>();
+    } else {
+      sel_wait<0>();
+    }
+    __syncthreads();
+    // the step sizes, once per (token, channel)
+    for (int i = threadIdx.x; i < n_tok * nch; i += SEL_THREADS) {
+      const int j = i / nch, k = i - j * nch;
+      float* p = b + j * row_w + 2 * N + k;
+      *p = sel_softplus(*p + hb_to_float(dtb[c0 + k]));
+    }
+    __syncthreads();
+    for (int j = 0; j < n_tok; j++) {
+      const float* row = b + j * row_w;
+      const float dtv = row[2 * N + cl], xv = row[2 * N + CPB + cl];
+      const float dx = dtv * xv;
+      float acc = 0.f;
+#pragma unroll
+      for (int i = 0; i < NPT; i++) {
+        const int n = ks + i * KS;
+        if (n < N) {
+          S[i] = fmaf(expf(dtv * rate[i]), S[i], dx * row[n]);
+          acc = fmaf(S[i], row[N + n], acc);
+        }
+      }
+      for (int o = KS >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (ks == 0) {
+        const float zz = row[2 * N + 2 * CPB + cl];
+        b[j * row_w + 2 * N + 2 * CPB + cl] = fmaf(dskip, xv, acc) * (zz / (1.f + expf(-zz)));
+      }
+    }
+    __syncthreads();
+    TO* out = (TO*)A.out;
+    for (int i = threadIdx.x; i < n_tok * nch; i += SEL_THREADS) {
+      const int j = i / nch, k = i - j * nch;
+      out[(size_t)(t0 + j0 + j) * A.ldo + c0 + k] = hb_from_float<TO>(b[j * row_w + 2 * N + 2 * CPB + k]);
+    }
+    __syncthreads();     // the buffer is asked for again two chunks on
+  }
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < NPT; i++) {
+      const int n = ks + i * KS;
+      if (n < N) st[n] = S[i];
+    }
+  }
+}
+
+// x, dt, z float32 [T][inner] (row strides ldx, lddt, ldz), bc float32 rows of B [N] | C [N] (stride ldbc); dt_bias [inner],
+// a_log [inner][N], d_skip [inner] in the element type w_dt; state float32 [slots][inner][N]; out [T][inner] in o_dt.
+HB_EXPORT int hb_selective_scan(const float* x, long ldx, const float* dt, long lddt, const float* bc, long ldbc, const float* z,
+                                long ldz, const void* dt_bias, const void* a_log, const void* d_skip, int w_dt, float* state,
+                                const int* q_start, const int* q_len, const int* slot, void* out, int o_dt, long ldo,
+                                int n_requests, int inner, int N, cudaStream_t s) {
+  if (n_requests <= 0 || inner <= 0) return 0;
+  if (N < 1 || N > 256) HB_FAIL("hb_selective_scan: %d states a channel (1 to 256 are supported)", N);
+  int KS = 1;
+  while (KS < 32 && (N + KS - 1) / KS > 4) KS <<= 1;
+  const int npt = (N + KS - 1) / KS, CPB = SEL_THREADS / KS;
+  SelArgs A = {x, ldx, dt, lddt, bc, ldbc, z, ldz, dt_bias, a_log, d_skip, state, q_start, q_len, slot, out, ldo, inner, N, KS};
+  dim3 grid((inner + CPB - 1) / CPB, n_requests);
+  if (grid.y > 65535) HB_FAIL("hb_selective_scan: the grid is too large");
+  const size_t smem = (size_t)2 * SEL_CH * (2 * N + 3 * CPB) * sizeof(float);
+#define SEL_LAUNCH(NPT)                                                                                      \
+  HB_DISPATCH_2(w_dt, o_dt, "hb_selective_scan", do {                                                        \
+    auto kern = selective_scan_kernel<TA, TB, NPT>;                                                          \
+    if (smem > 40 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    hb_launch(kern, grid, dim3(SEL_THREADS), smem, s, A);                                                    \
+  } while (0))
+  if (npt <= 1) SEL_LAUNCH(1);
+  else if (npt <= 2) SEL_LAUNCH(2);
+  else if (npt <= 4) SEL_LAUNCH(4);
+  else SEL_LAUNCH(8);
+#undef SEL_LAUNCH
+  HB_CHECK_LAUNCH("hb_selective_scan");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// The residual row after a sublayer, in one pass:
+//     u = y                                                        a sublayer's plain result (or nothing)
+//       + mix * (a / rms(a) * wa + b / rms(b) * wb)                two side-by-side results, each normed over the row first
+//     v = alpha * x + u
+//     x <- v / rms(v) * w       (w given: the norm AFTER the sum, its weight as stored, or as one plus what is stored;
+//                                no w: x <- v)
+// and, where asked, a copy of the new x in the compute element type for the products that read it next. Root mean squares
+// with eps inside the root; everything 32-bit; one block a row, the row kept in shared memory between the passes.
+// ---------------------------------------------------------------------------------------------------------------------
+template <typename TW, typename TO>
+__global__ void __launch_bounds__(256) residual_norm_kernel(float* __restrict__ x, const float* __restrict__ y,
+                                                            const float* __restrict__ a, const float* __restrict__ b,
+                                                            const TW* __restrict__ wa, const TW* __restrict__ wb, float mix,
+                                                            float pair_eps, float alpha, const float* __restrict__ w,
+                                                            float eps, TO* __restrict__ xb, int W) {
+  extern __shared__ float rn_row[];      // [W], then 32 floats for the sums
+  float* red = rn_row + W;
+  hb_pdl_launch();
+  hb_pdl_wait();
+  const size_t base = (size_t)blockIdx.x * W;
+  float fa = 0.f, fb = 0.f;
+  if (a) {
+    float sa = 0.f, sb = 0.f;
+    for (int i = threadIdx.x; i < W; i += 256) {
+      const float va = a[base + i], vb = b[base + i];
+      sa = fmaf(va, va, sa);
+      sb = fmaf(vb, vb, sb);
+    }
+    fa = rsqrtf(hb_block_sum(sa, red) / (float)W + pair_eps);
+    fb = rsqrtf(hb_block_sum(sb, red) / (float)W + pair_eps);
+  }
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < W; i += 256) {
+    float u = y ? y[base + i] : 0.f;
+    if (a) u += mix * (a[base + i] * fa * hb_to_float(wa[i]) + b[base + i] * fb * hb_to_float(wb[i]));
+    const float v = fmaf(alpha, x[base + i], u);
+    rn_row[i] = v;
+    ss = fmaf(v, v, ss);
+  }
+  float f = 1.f;
+  if (w) f = rsqrtf(hb_block_sum(ss, red) / (float)W + eps);
+  for (int i = threadIdx.x; i < W; i += 256) {
+    const float v = w ? rn_row[i] * f * w[i] : rn_row[i];
+    x[base + i] = v;
+    if (xb) xb[base + i] = hb_from_float<TO>(v);
+  }
+}
+
+// x float32 [T][W] in place; y, a, b float32 [T][W] or null (a and b together); wa, wb [W] in pw_dt; w float32 [W] or null;
+// xb [T][W] in xb_dt or null.
+HB_EXPORT int hb_residual_norm(float* x, const float* y, const float* a, const float* b, const void* wa, const void* wb,
+                               int pw_dt, float mix, float pair_eps, float alpha, const float* w, float eps, void* xb,
+                               int xb_dt, int T, int W, cudaStream_t s) {
+  if (T <= 0) return 0;
+  if ((a != nullptr) != (b != nullptr) || (a && (!wa || !wb))) HB_FAIL("hb_residual_norm: a pair needs both rows and both weights");
+  const size_t smem = (size_t)(W + 32) * sizeof(float);
+  if (smem > 200 * 1024) HB_FAIL("hb_residual_norm: a row of %d does not fit shared memory", W);
+  if (!a) pw_dt = HB_F32;
+  if (!xb) xb_dt = HB_F32;
+  HB_DISPATCH_2(pw_dt, xb_dt, "hb_residual_norm", do {
+    auto kern = residual_norm_kernel<TA, TB>;
+    if (smem > 40 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    hb_launch(kern, dim3(T), dim3(256), smem, s, x, y, a, b, (const TA*)wa, (const TA*)wb, mix, pair_eps, alpha, w, eps, (TB*)xb, W);
+  } while (0));
+  HB_CHECK_LAUNCH("hb_residual_norm");
+  return 0;
+}

@@ -32,7 +32,7 @@ LIBRARIES: Dict[str, List[str]] = {
     "core": ["core.cu"],
     "mixers": ["mixers_entry.cu", "delta_rule.cu", "attention_window.cu", "attention_window_flash.cu"],
     "seqmix": ["seqmix_entry.cu", "attention_masked.cu", "attention_masked_flash.cu", "attention_masked_heads.cu", "latent.cu", "gla.cu"],
-    "hybrid": ["hybrid_entry.cu", "hyper_streams.cu", "ssd.cu", "moe.cu"],
+    "hybrid": ["hybrid_entry.cu", "hyper_streams.cu", "ssd.cu", "moe.cu", "selective_scan.cu"],
     "fast": ["fast_entry.cu", "gemm_tc.cu", "gemm_stream.cu", "gemm_stream_consumers.cu", "gemm_rows.cu", "attention_fast.cu", "attention_prefill.cu", "attention_prefill_tc.cu", "wait_selftest.cu"],
 }
 HEADERS = ["common.cuh", "tc_common.cuh", "gemm_stream_static.h"]

@@ -25,7 +25,7 @@ _SIGS = {
         "hb_rmsnorm": [_p, _p, _i, _p, _i, _p, _i, _i, _f, _p],
         "hb_gemm_simt": [_p, _i, _l, _p, _i, _l, _p, _i, _l, _i, _i, _i, _i, _p],
         "hb_swiglu": [_p, _i, _l, _p, _i, _l, _i, _i, _i, _p],
-        "hb_rope_table": [_p, _p, _i, _i, _p],
+        "hb_rope_table": [_p, _p, _i, _i, C.c_double, _p],
         "hb_rope_kv": [_p, _i, _l, _p, _p, _p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p],
         "hb_attn_rows": [_p, _i, _p, _p, _i, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _i, _p],
         "hb_attn_merge": [_p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _p, _i, _p],
@@ -35,7 +35,8 @@ _SIGS = {
         "hb_embed_pos": [_p, _p, _i, _p, _p, _p, _i, _i, _f, _p],
         "hb_layernorm": [_p, _p, _p, _i, _p, _i, _p, _i, _i, _f, _p],
         "hb_gated_act": [_p, _i, _l, _p, _i, _l, _i, _i, _i, _i, _p],
-        "hb_rope_norm_store": [_p, _l, _i, _i, _i, _p, _p, _p, _i, _i, _i, _i, _f, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p],
+        "hb_rope_norm_store": [_p, _l, _i, _i, _i, _p, _p, _p, _i, _i, _i, _i, _f, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _p, _i,
+                               _f, _p],
         "hb_polynorm": [_p, _l, _p, _i, _l, _i, _i, _f, _f, _f, _f, _f, _p],
         "hb_scale_add": [_p, _p, _l, _p, _i, _i, _i, _p],
         "hb_bias_act": [_p, _l, _p, _i, _p, _i, _l, _i, _i, _i, _p],
@@ -45,8 +46,8 @@ _SIGS = {
     "seqmix": {
         "hb_attn_masked": [_p, _i, _l, _p, _l, _p, _l, _i, _p, _i, _p, _p, _p, _p, _l, _i, _i, _p, _i, _l, _i, _i, _i, _i, _i,
                            _i, _i, _i, _i, _i, _f, _p, _i, _p, _l, _p, _i, _p],
-        "hb_latent_prepare": [_p, _l, _i, _i, _i, _p, _p, _i, _p, _p, _p, _i, _f, _p, _p, _i, _i, _i, _i, _i, _i, _p],
-        "hb_heads_linear": [_p, _l, _l, _p, _i, _p, _i, _l, _l, _i, _i, _i, _i, _p, _l, _i, _i, _i, _p, _p, _p, _p, _i, _p],
+        "hb_latent_prepare": [_p, _l, _i, _i, _i, _p, _p, _i, _p, _p, _p, _i, _f, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p],
+        "hb_heads_linear": [_p, _l, _l, _p, _i, _p, _i, _l, _l, _i, _i, _i, _i, _p, _l, _i, _i, _i, _p, _p, _p, _p, _i, _i, _i, _p],
         "hb_gather_rows": [_p, _i, _p, _p, _i, _i, _i, _p],
         "hb_attn_masked_flash_supported": [_i, _i],
         "hb_attn_masked_heads_supported": [_i, _i, _i, _i, _i],
@@ -66,13 +67,15 @@ _SIGS = {
         "hb_ssd_conv": [_p, _l, _i, _p, _p, _i, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p],
         "hb_ssd_scan": [_p, _l, _p, _l, _p, _p, _p, _i, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _p, _p],
         "hb_ssd_gate_norm": [_p, _p, _l, _p, _i, _p, _i, _i, _i, _i, _f, _p],
-        "hb_moe_route": [_p, _i, _l, _p, _i, _p, _p, _i, _i, _i, _i, _p],
-        "hb_moe_gate_up_rows": [_p, _i, _l, _p, _i, _p, _p, _p, _i, _i, _i, _i, _p],
+        "hb_selective_scan": [_p, _l, _p, _l, _p, _l, _p, _l, _p, _p, _p, _i, _p, _p, _p, _p, _p, _i, _l, _i, _i, _i, _p],
+        "hb_residual_norm": [_p, _p, _p, _p, _p, _p, _i, _f, _f, _f, _p, _f, _p, _i, _i, _i, _p],
+        "hb_moe_route": [_p, _i, _l, _p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _p],
+        "hb_moe_gate_up_rows": [_p, _i, _l, _p, _i, _p, _p, _p, _i, _i, _i, _i, _i, _p],
         "hb_moe_down_rows": [_p, _i, _p, _i, _p, _p, _l, _i, _i, _i, _i, _p],
         "hb_moe_sort": [_p, _p, _p, _p, _i, _i, _p],
         "hb_moe_grouped": [_p, _i, _l, _p, _i, _p, _i, _p, _p, _i, _i, _i, _p],
         "hb_moe_gather": [_p, _i, _l, _p, _p, _i, _i, _i, _p],
-        "hb_moe_act": [_p, _p, _p, _p, _i, _i, _i, _p],
+        "hb_moe_act": [_p, _p, _p, _p, _i, _i, _i, _i, _p],
         "hb_moe_combine": [_p, _p, _p, _l, _i, _i, _i, _p],
     },
     "mixers": {
@@ -392,13 +395,13 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor, group: int) -> torch.Tensor
     return out
 
 
-def rope_table(inv_freq: torch.Tensor, n_pos: int) -> torch.Tensor:
-    """(cos, sin) float32 [n_pos, len(inv_freq), 2] of angle = float32(p) * inv_freq[i]."""
+def rope_table(inv_freq: torch.Tensor, n_pos: int, magnitude: float = 1.0) -> torch.Tensor:
+    """(cos, sin) float32 [n_pos, len(inv_freq), 2] of angle = float32(p) * inv_freq[i], both times `magnitude`."""
     _need_cuda(inv_freq)
     assert inv_freq.dtype == torch.float32 and inv_freq.is_contiguous()
     half = inv_freq.numel()
     table = torch.empty(n_pos, half, 2, dtype=torch.float32, device=inv_freq.device)
-    _call("core", "hb_rope_table", inv_freq.data_ptr(), table.data_ptr(), n_pos, half, _stream())
+    _call("core", "hb_rope_table", inv_freq.data_ptr(), table.data_ptr(), n_pos, half, float(magnitude), _stream())
     return table
 
 
@@ -768,15 +771,47 @@ def linear_gated(a: torch.Tensor, w_gate_up: "Weight", act_out: torch.Tensor, gr
 _rope_tables = {}
 
 
-def shared_rope_table(dims: int, base: float, n_pos: int, device) -> torch.Tensor:
-    """(cos, sin) float32 [n_pos, dims / 2, 2] of the angles p * base^(-2i / dims): one table per (dims, base, n_pos,
-    device), shared by every part that asks (the frequencies are computed in float64 and rounded to float32)."""
-    key = (int(dims), float(base), int(n_pos), str(device))
+def rope_frequencies(dims: int, base: float, scaling=None):
+    """(frequencies float64 [dims / 2], magnitude): f_i = base^(-2i / dims), rescaled by `scaling` (a mapping or None):
+
+    kind "wavelength_bands" (factor, low, high, original): with the wavelength l = 2 pi / f, f stays where l < original /
+        high, becomes f / factor where l > original / low, and between the two is (1 - s) f / factor + s f with
+        s = (original / l - low) / (high - low); magnitude 1.
+    kind "yarn" (factor, original, fast, slow): with d(t) = dims ln(original / (2 pi t)) / (2 ln base), lo = max(floor(d(fast)),
+        0), hi = min(ceil(d(slow)), dims - 1) and r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), the frequency is
+        r_i f_i / factor + (1 - r_i) f_i, and cos and sin are both multiplied by the magnitude 0.1 ln(factor) + 1."""
+    import math
+
+    i = torch.arange(0, dims // 2, dtype=torch.float64)
+    f = torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / dims)
+    if not scaling:
+        return f, 1.0
+    kind = scaling.get("kind")
+    if kind == "wavelength_bands":
+        factor, low, high, orig = (float(scaling[k]) for k in ("factor", "low", "high", "original"))
+        wl = 2.0 * math.pi / f
+        s = (orig / wl - low) / (high - low)
+        mid = (1.0 - s) * f / factor + s * f
+        return torch.where(wl < orig / high, f, torch.where(wl > orig / low, f / factor, mid)), 1.0
+    if kind == "yarn":
+        factor, orig, fast, slow = (float(scaling[k]) for k in ("factor", "original", "fast", "slow"))
+        d_of = lambda t: dims * math.log(orig / (2.0 * math.pi * t)) / (2.0 * math.log(float(base)))
+        lo, hi = max(math.floor(d_of(fast)), 0), min(math.ceil(d_of(slow)), dims - 1)
+        ramp = torch.clamp((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+        return f / factor * ramp + f * (1.0 - ramp), 0.1 * math.log(factor) + 1.0
+    raise KernelError(f"rotary scaling of kind {kind!r} is not known (known: 'wavelength_bands', 'yarn')")
+
+
+def shared_rope_table(dims: int, base: float, n_pos: int, device, scaling=None) -> torch.Tensor:
+    """(cos, sin) float32 [n_pos, dims / 2, 2] of the angles p * f_i, f_i = base^(-2i / dims) rescaled by `scaling` (see
+    rope_frequencies; the magnitude is in the table): one table per (dims, base, scaling, n_pos, device), shared by every
+    part that asks (the frequencies are computed in float64 and rounded to float32)."""
+    skey = tuple(sorted((k, v) for k, v in scaling.items())) if scaling else None
+    key = (int(dims), float(base), skey, int(n_pos), str(device))
     t = _rope_tables.get(key)
     if t is None:
-        i = torch.arange(0, dims, 2, dtype=torch.float64)
-        inv = torch.pow(torch.tensor(float(base), dtype=torch.float64), -i / dims).to(torch.float32)
-        t = _rope_tables[key] = rope_table(inv.to(device), n_pos)
+        f, mag = rope_frequencies(int(dims), float(base), scaling)
+        t = _rope_tables[key] = rope_table(f.to(torch.float32).to(device), n_pos, mag)
     return t
 
 
@@ -786,11 +821,13 @@ PAIRINGS = {"half": 0, "interleaved": 1}
 def rope_norm_store(proj: torch.Tensor, offsets, positions: torch.Tensor, slot_map: Optional[torch.Tensor],
                     table: torch.Tensor, rot: int, pairing: str, unit_norm: bool, eps: float, q_out: torch.Tensor,
                     k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], n_heads: int, n_kv_heads: int,
-                    dim: int, vdim: int, page_size: int, rot_off: int = 0) -> torch.Tensor:
+                    dim: int, vdim: int, page_size: int, rot_off: int = 0, row_norm=None, row_norm_eps: float = 0.0) -> torch.Tensor:
     """From a float32 projection result whose rows hold q, k, v at the column `offsets` (q, k, v): q and k rotated on
     the `rot` dimensions from `rot_off` on (pairing "half": (i, i + rot/2); "interleaved": (2i, 2i + 1)) and, with unit_norm,
     divided by their root mean square over `dim`; q to q_out [T, n_heads * dim], k and v (vdim wide, raw) to their page
-    slots. slot_map None: q alone."""
+    slots. slot_map None: q alone. row_norm (wq [n_heads * dim], wk [n_kv_heads * dim]): before the rotation the whole
+    q row and the whole k row are divided by their root mean square (row_norm_eps inside the root) and multiplied by the
+    weights, column by column."""
     _need_cuda(proj, positions, slot_map, table, q_out, k_cache, v_cache)
     _rows_contiguous(proj, "rope_norm_store in")
     T = proj.shape[0]
@@ -800,10 +837,15 @@ def rope_norm_store(proj: torch.Tensor, offsets, positions: torch.Tensor, slot_m
         assert k_cache.dtype == v_cache.dtype == q_out.dtype and k_cache.is_contiguous() and v_cache.is_contiguous()
         assert k_cache.shape[-1] == dim and v_cache.shape[-1] == vdim
     q_off, k_off, v_off = (int(o) for o in offsets)
+    wq_pre, wk_pre = row_norm if row_norm is not None else (None, None)
+    if wq_pre is not None:
+        _need_cuda(wq_pre, wk_pre)
+        assert wq_pre.dtype == wk_pre.dtype and wq_pre.numel() == n_heads * dim and wk_pre.numel() == n_kv_heads * dim
     _call("core", "hb_rope_norm_store", proj.data_ptr(), proj.stride(0), q_off, k_off, v_off, positions.data_ptr(),
           _ptr(slot_map), table.data_ptr(), int(rot), int(rot_off), PAIRINGS[pairing], 1 if unit_norm else 0, float(eps), q_out.data_ptr(),
           _ptr(k_cache) if slot_map is not None else None, _ptr(v_cache) if slot_map is not None else None, _dt(q_out), T,
-          n_heads, n_kv_heads, dim, vdim, page_size, _stream())
+          n_heads, n_kv_heads, dim, vdim, page_size, _ptr(wq_pre), _ptr(wk_pre), _dt(wq_pre) if wq_pre is not None else 0,
+          float(row_norm_eps), _stream())
     return q_out
 
 
@@ -894,10 +936,11 @@ def attention_masked(q, k_cache, v_cache, batch, group: int, out, n_heads: int, 
 
 def latent_prepare(proj: torch.Tensor, offsets, wq: torch.Tensor, wc: torch.Tensor, positions, slot_map, table, rot: int,
                    eps: float, cq_out: torch.Tensor, cache: Optional[torch.Tensor], q_rank: int, kv_rank: int, rot_dim: int,
-                   page_size: int) -> torch.Tensor:
+                   page_size: int, pairing: str = "interleaved") -> torch.Tensor:
     """From a float32 projection result with the raw query latent, the raw key/value latent and the raw rotated key part
     at the column `offsets`: the query latent / rms * wq to cq_out [T, q_rank]; the key/value latent / rms * wc and the
-    rotated key part (pairs (2i, 2i + 1)) to the token's row of `cache` [page, 1, page_size, kv_rank + rot_dim]."""
+    rotated key part (pairing "interleaved": pairs (2i, 2i + 1); "half": (i, i + rot / 2)) to the token's row of `cache`
+    [page, 1, page_size, kv_rank + rot_dim]."""
     _need_cuda(proj, wq, wc, positions, slot_map, table, cq_out, cache)
     _rows_contiguous(proj, "latent_prepare in")
     T = proj.shape[0]
@@ -908,16 +951,18 @@ def latent_prepare(proj: torch.Tensor, offsets, wq: torch.Tensor, wc: torch.Tens
     a, b, c = (int(o) for o in offsets)
     _call("seqmix", "hb_latent_prepare", proj.data_ptr(), proj.stride(0), a, b, c, _ptr(wq), wc.data_ptr(), _dt(wc),
           positions.data_ptr(), _ptr(slot_map), table.data_ptr(), int(rot), float(eps), cq_out.data_ptr(),
-          _ptr(cache) if slot_map is not None else None, _dt(cq_out), T, q_rank, kv_rank, rot_dim, page_size, _stream())
+          _ptr(cache) if slot_map is not None else None, _dt(cq_out), T, q_rank, kv_rank, rot_dim, page_size, PAIRINGS[pairing],
+          _stream())
     return cq_out
 
 
 def heads_linear(a: torch.Tensor, a_head: int, wt: torch.Tensor, out: torch.Tensor, o_head: int, gate=None,
                  gate_offset: int = 0, tail: int = 0, rot: int = 0, positions=None, table=None, batch=None,
-                 row_limit: int = 0) -> torch.Tensor:
+                 row_limit: int = 0, pairing: str = "interleaved", gate_per_head: bool = False) -> torch.Tensor:
     """out[t, h * o_head + n] = sum_k a[t, h * a_head + k] wt[h, k, n] for every head h (a float32, 32-bit sums),
-    optionally times sigmoid(gate[t, gate_offset + h * N + n]); with `tail`, the tail columns behind a head's K inputs
-    are rotated on their first `rot` (pairs (2i, 2i + 1)) by the row's position and copied behind its N outputs. With
+    optionally times sigmoid(gate[t, gate_offset + h * N + n]) (gate_per_head: of gate[t, gate_offset + h]); with `tail`,
+    the tail columns behind a head's K inputs are rotated on their first `rot` (pairs (2i, 2i + 1), or (i, i + rot / 2)
+    with pairing "half") by the row's position and copied behind its N outputs. With
     `batch` and `row_limit`, rows of requests that bring row_limit rows or more are left alone (another path has them)."""
     _need_cuda(a, wt, out, gate, positions, table)
     _rows_contiguous(a, "heads_linear a")
@@ -931,7 +976,7 @@ def heads_linear(a: torch.Tensor, a_head: int, wt: torch.Tensor, out: torch.Tens
           _dt(out), out.stride(0), int(o_head), T, H, K, N, _ptr(gate), gate.stride(0) if gate is not None else 0,
           int(gate_offset), int(tail), int(rot), _ptr(positions), _ptr(table),
           batch.row_request.data_ptr() if row_limit else None, batch.req_q_len.data_ptr() if row_limit else None, int(row_limit),
-          _stream())
+          PAIRINGS[pairing], 1 if gate_per_head else 0, _stream())
     return out
 
 
@@ -969,18 +1014,20 @@ def masked_flash_supported(dim: int, vdim: int) -> bool:
 
 def attention_flash_tokens(q, keys, values, batch, request: int, out, n_heads: int, n_kv_heads: int, dim: int, vdim: int,
                            scale: float, gate=None, gate_offset: int = 0, gate_per_head: bool = False, window: int = 0,
-                           first_pos: int = 0) -> torch.Tensor:
+                           first_pos: int = 0, sink: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal attention of the rows of ONE request of the batch (index `request`) over keys and values made for its
     context in token-major buffers: keys [n, >= n_kv_heads * dim] and values [n, >= n_kv_heads * vdim] (views of wider
     rows are fine), row t the token at position first_pos + t. With `window` a row at position i sees the keys j with
-    0 <= i - j < window (first_pos must not lie behind the first key that the request's first row sees). bfloat16; the
-    tensor-core kernel of csrc/attention_masked_flash.cu."""
-    _need_cuda(q, keys, values, out, gate)
+    0 <= i - j < window (first_pos must not lie behind the first key that the request's first row sees). sink: float32
+    [n_heads], joins the softmax's denominator as exp(sink). bfloat16; the tensor-core kernel of
+    csrc/attention_masked_flash.cu."""
+    _need_cuda(q, keys, values, out, gate, sink)
+    assert sink is None or (sink.dtype == torch.float32 and sink.numel() == n_heads and sink.is_contiguous())
     n = keys.shape[0]
     assert q.dtype == keys.dtype == values.dtype == torch.bfloat16 and keys.stride(1) == values.stride(1) == 1
     _call("seqmix", "hb_attn_masked_flash", q.data_ptr(), q.stride(0), keys.data_ptr(), keys.stride(0), dim, 0, values.data_ptr(),
           values.stride(0), vdim, 0, _identity_table(q.device, n).data_ptr() - 4 * int(first_pos), 0, batch.req_q_start.data_ptr(),
-          batch.req_q_len.data_ptr(), batch.req_ctx_len.data_ptr(), int(request), 1, int(batch.h_q_len[request]), 1, None,
+          batch.req_q_len.data_ptr(), batch.req_ctx_len.data_ptr(), int(request), 1, int(batch.h_q_len[request]), 1, _ptr(sink),
           _ptr(gate), gate.stride(0) if gate is not None else 0, int(gate_offset), (2 if gate_per_head else 1) if gate is not None else 0,
           out.data_ptr(), _dt(out), out.stride(0), n_heads, n_kv_heads, dim, vdim, 1, 1 if window else 0, int(window), 0, 0,
           float(scale), _stream())
@@ -1146,24 +1193,86 @@ def ssd_gate_norm(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, out: t
     return out
 
 
-def moe_route(xn: torch.Tensor, router: torch.Tensor, top: int):
-    """(expert int32 [T, top], score float32 [T, top]): the `top` experts with the largest sigmoid(router @ row), 32-bit
-    sums; the largest first, ties to the lower index."""
-    _need_cuda(xn, router)
+def selective_scan(x: torch.Tensor, dt: torch.Tensor, bc: torch.Tensor, z: torch.Tensor, dt_bias: torch.Tensor,
+                   a_log: torch.Tensor, d_skip: torch.Tensor, state: torch.Tensor, batch, out: torch.Tensor) -> torch.Tensor:
+    """The selective recurrence with a decay per (channel, state) pair over the step's rows, request by request, from and
+    into each request's state slot (csrc/selective_scan.cu). x, dt, z float32 [T, inner] (views of wider rows are fine):
+    the convolved input, the step-size product without its bias, the gate's pre-activation; bc float32 [T, 2N]: B then C;
+    dt_bias [inner], a_log [inner, N], d_skip [inner]; state float32 [slots, inner, N]. out [T, inner] = (sum_n S C + D x)
+    silu(z), rounded once."""
+    _need_cuda(x, dt, bc, z, dt_bias, a_log, d_skip, state, out)
+    for t, what in ((x, "x"), (dt, "dt"), (bc, "bc"), (z, "z"), (out, "out")):
+        _rows_contiguous(t, "selective_scan " + what)
+    T, inner = x.shape
+    N = a_log.shape[1]
+    assert x.dtype == dt.dtype == bc.dtype == z.dtype == state.dtype == torch.float32 and state.is_contiguous()
+    assert dt.shape == z.shape == out.shape == (T, inner) and bc.shape == (T, 2 * N) and state.shape[1:] == (inner, N)
+    assert a_log.is_contiguous() and a_log.shape[0] == inner and dt_bias.numel() == d_skip.numel() == inner
+    assert dt_bias.dtype == a_log.dtype == d_skip.dtype
+    _call("hybrid", "hb_selective_scan", x.data_ptr(), x.stride(0), dt.data_ptr(), dt.stride(0), bc.data_ptr(), bc.stride(0),
+          z.data_ptr(), z.stride(0), dt_bias.data_ptr(), a_log.data_ptr(), d_skip.data_ptr(), _dt(a_log), state.data_ptr(),
+          batch.req_q_start.data_ptr(), batch.req_q_len.data_ptr(), batch.req_state_slot.data_ptr(), out.data_ptr(), _dt(out),
+          out.stride(0), batch.n_requests, inner, N, _stream())
+    return out
+
+
+class NormedPair:
+    """Two side-by-side results that have yet to be joined: mix * (a / rms(a) * wa + b / rms(b) * wb), a and b float32
+    [T, W], the weights [W], eps inside the roots. `residual_norm` joins them on its way over the row."""
+    __slots__ = ("a", "b", "wa", "wb", "mix", "eps")
+
+    def __init__(self, a, b, wa, wb, mix, eps):
+        self.a, self.b, self.wa, self.wb, self.mix, self.eps = a, b, wa, wb, float(mix), float(eps)
+
+
+def residual_norm(x: torch.Tensor, y: Optional[torch.Tensor] = None, pair: Optional[NormedPair] = None, alpha: float = 1.0,
+                  weight: Optional[torch.Tensor] = None, eps: float = 0.0, rounded: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The residual rows x float32 [T, W] after a sublayer, in place and in one pass: v = alpha * x + y + the joined `pair`
+    (either may be absent); with `weight` (float32 [W]) x <- v / rms(v) * weight, the norm AFTER the sum, else x <- v.
+    rounded: a tensor [T, W] of the compute element type that receives a copy of the new x."""
+    _need_cuda(x, y, weight, rounded)
+    T, W = x.shape
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    assert y is None or (y.dtype == torch.float32 and y.is_contiguous() and y.shape == (T, W))
+    assert weight is None or (weight.dtype == torch.float32 and weight.is_contiguous() and weight.numel() == W)
+    assert rounded is None or (rounded.is_contiguous() and rounded.shape == (T, W))
+    a = b = wa = wb = None
+    mix = pe = 0.0
+    if pair is not None:
+        a, b, wa, wb, mix, pe = pair.a, pair.b, pair.wa, pair.wb, pair.mix, pair.eps
+        _need_cuda(a, b, wa, wb)
+        assert a.dtype == b.dtype == torch.float32 and a.is_contiguous() and b.is_contiguous() and a.shape == b.shape == (T, W)
+        assert wa.dtype == wb.dtype and wa.numel() == wb.numel() == W and wa.is_contiguous() and wb.is_contiguous()
+    _call("hybrid", "hb_residual_norm", x.data_ptr(), _ptr(y), _ptr(a), _ptr(b), _ptr(wa), _ptr(wb),
+          _dt(wa) if wa is not None else 0, float(mix), float(pe), float(alpha), _ptr(weight), float(eps), _ptr(rounded),
+          _dt(rounded) if rounded is not None else 0, T, W, _stream())
+    return x
+
+
+MOE_SCORES = {"sigmoid": 0, "softmax_chosen": 1}
+
+
+def moe_route(xn: torch.Tensor, router: torch.Tensor, top: int, bias: Optional[torch.Tensor] = None, score: str = "sigmoid"):
+    """(expert int32 [T, top], weight float32 [T, top]): the `top` experts with the largest z = router @ row (+ bias), 32-bit
+    sums; the largest first, ties to the lower index. score "sigmoid": the weights are sigmoid(z) of the chosen ones;
+    "softmax_chosen": the softmax over the chosen logits alone."""
+    _need_cuda(xn, router, bias)
+    assert bias is None or (bias.dtype == router.dtype and bias.numel() == router.shape[0] and bias.is_contiguous())
     _rows_contiguous(xn, "moe_route in")
     T, (E, W) = xn.shape[0], router.shape
     assert router.is_contiguous() and xn.shape[1] == W
     expert = torch.empty(T, top, dtype=torch.int32, device=xn.device)
-    score = torch.empty(T, top, dtype=torch.float32, device=xn.device)
-    _call("hybrid", "hb_moe_route", xn.data_ptr(), _dt(xn), xn.stride(0), router.data_ptr(), _dt(router), expert.data_ptr(),
-          score.data_ptr(), T, W, E, int(top), _stream())
-    return expert, score
+    weight = torch.empty(T, top, dtype=torch.float32, device=xn.device)
+    _call("hybrid", "hb_moe_route", xn.data_ptr(), _dt(xn), xn.stride(0), router.data_ptr(), _ptr(bias), _dt(router),
+          expert.data_ptr(), weight.data_ptr(), T, W, E, int(top), MOE_SCORES[score], _stream())
+    return expert, weight
 
 
 def moe_rows(xn: torch.Tensor, wgu: torch.Tensor, wdown: torch.Tensor, expert: torch.Tensor, score: torch.Tensor,
-             y: torch.Tensor) -> torch.Tensor:
+             y: torch.Tensor, at_output: bool = False) -> torch.Tensor:
     """y += sum over a row's chosen experts of Wd_e (silu(s Wg_e h) * (s Wu_e h)), row by row with nothing sorted and
-    nothing on the host. wgu [E, 2F, W] (gate rows, then up rows), wdown [E, W, F], y float32 [T, W]."""
+    nothing on the host. wgu [E, 2F, W] (gate rows, then up rows), wdown [E, W, F], y float32 [T, W]. at_output: the
+    weight multiplies the expert's result instead of its input, Wd_e (s silu(Wg_e h) * (Wu_e h))."""
     _need_cuda(xn, wgu, wdown, expert, score, y)
     _rows_contiguous(xn, "moe_rows in")
     _rows_contiguous(y, "moe_rows out")
@@ -1173,7 +1282,7 @@ def moe_rows(xn: torch.Tensor, wgu: torch.Tensor, wdown: torch.Tensor, expert: t
     assert wgu.is_contiguous() and wdown.is_contiguous() and wdown.shape == (E, W, F) and y.dtype == torch.float32
     act = torch.empty(T * top, F, dtype=xn.dtype, device=xn.device)
     _call("hybrid", "hb_moe_gate_up_rows", xn.data_ptr(), _dt(xn), xn.stride(0), wgu.data_ptr(), _dt(wgu), expert.data_ptr(),
-          score.data_ptr(), act.data_ptr(), T, W, F, top, _stream())
+          score.data_ptr(), act.data_ptr(), T, W, F, top, 1 if at_output else 0, _stream())
     _call("hybrid", "hb_moe_down_rows", act.data_ptr(), _dt(act), wdown.data_ptr(), _dt(wdown), expert.data_ptr(), y.data_ptr(),
           y.stride(0), T, W, F, top, _stream())
     return y
@@ -1216,11 +1325,13 @@ def moe_gather(xn: torch.Tensor, src: torch.Tensor, top: int) -> torch.Tensor:
     return out
 
 
-def moe_act(gu: torch.Tensor, src: torch.Tensor, score: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[r] = silu(s g) * (s u) of the sorted rows' float32 [g | u], s the score of the row's pair."""
+def moe_act(gu: torch.Tensor, src: torch.Tensor, score: torch.Tensor, out: torch.Tensor, at_output: bool = False) -> torch.Tensor:
+    """out[r] = silu(s g) * (s u) of the sorted rows' float32 [g | u], s the score of the row's pair; with at_output
+    s silu(g) * u (the weight of the expert's result, brought in before the linear down product)."""
     pairs, F = out.shape
     assert gu.dtype == torch.float32 and gu.is_contiguous() and gu.shape == (pairs, 2 * F) and out.is_contiguous()
-    _call("hybrid", "hb_moe_act", gu.data_ptr(), src.data_ptr(), score.data_ptr(), out.data_ptr(), _dt(out), pairs, F, _stream())
+    _call("hybrid", "hb_moe_act", gu.data_ptr(), src.data_ptr(), score.data_ptr(), out.data_ptr(), _dt(out), pairs, F,
+          1 if at_output else 0, _stream())
     return out
 
 

@@ -12,6 +12,7 @@ import torch
 from ..kernels import ops
 from ..weights import ParamSpec
 from . import planes
+from .norm import RMSNorm
 from .registry import Part, build_part, register_part, to_compute
 
 
@@ -322,7 +323,94 @@ class HyperConnectionBlock(Part):
         return PreparedNorm(next_norm, rows) if rows is not None else None
 
 
+class RoundedRows:
+    """What a post-norm layer leaves for the next one: the residual rows `x` as it wrote them, rounded to the compute
+    element type on the way (`rows`), so that the next layer's products need no pass over x of their own."""
+
+    def __init__(self, x, rows):
+        self.x, self.rows = x, rows
+
+
+class PostNormBlock(Part):
+    """The norm AFTER the sum: x <- norm1(alpha * x + mixer(x)), then x <- norm2(alpha * x + feed_forward(x)). The sublayers
+    read the residual rows themselves (rounded to the compute element type for their products; the 32-bit engine reads x as
+    it is), not a normed copy, and alpha multiplies the residual, not the sublayer. The feed-forward with its norm is
+    optional (a layer that gives no `feed_forward` part has the first half only).
+
+    The scaled sum, the norm and the rounded copy for the next reader are one pass over the row (ops.residual_norm); a
+    mixer that offers `forward_pair` (two side-by-side results that are normed and joined) has its join in the same pass.
+    A norm part of another kind than the RMS norm is run as it is, on the summed rows.
+
+    params: layer (the LayerSpec), hidden_size, alpha (default 1)."""
+
+    SLOTS = {"mixer": "mixer", "mixer_norm": "norm", "feed_forward": "feed_forward", "feed_forward_norm": "norm"}
+    OPTIONAL = ("feed_forward", "feed_forward_norm")
+    takes_pending = True
+
+    def __init__(self, params, ctx, prefix=""):
+        super().__init__(params, ctx, prefix)
+        layer = params["layer"]
+        self.has_ff = "feed_forward" in layer.parts
+        slots = {n: r for n, r in self.SLOTS.items() if self.has_ff or n not in self.OPTIONAL}
+        self.parts = build_slots(self, layer, slots, ctx, prefix)
+        if not self.has_ff:
+            self.feed_forward = self.feed_forward_norm = None
+        self.hidden, self.alpha = int(params["hidden_size"]), float(params.get("alpha", 1.0))
+
+    def param_specs(self):
+        return [s for p in self.parts for s in p.param_specs()]
+
+    def load(self, tensors):
+        for p in self.parts:
+            p.load(tensors)
+
+    def weight_bytes(self):
+        return sum(p.weight_bytes() for p in self.parts)
+
+    def _rows(self, x, carry):
+        """The rows the sublayers' products read: x itself in the 32-bit engine, else its rounded copy."""
+        if self.ctx.dtype == torch.float32:
+            return x
+        if isinstance(carry, RoundedRows) and carry.x is x:
+            return carry.rows
+        return ops.convert(x, self.ctx.dtype)
+
+    def _close(self, x, norm, y=None, pair=None):
+        """x <- norm(alpha * x + y + pair); returns the rounded copy of the new x (None in the 32-bit engine)."""
+        rounded = None if self.ctx.dtype == torch.float32 else torch.empty(x.shape, dtype=self.ctx.dtype, device=x.device)
+        w = getattr(norm, "weight", None)
+        if isinstance(norm, RMSNorm) and w is not None and w.dtype == torch.float32:
+            ops.residual_norm(x, y, pair, self.alpha, w, norm.eps, rounded)
+            return rounded
+        ops.residual_norm(x, y, pair, self.alpha)
+        x.copy_(norm.forward(x, out=torch.empty_like(x)))
+        return None if rounded is None else ops.convert(x, self.ctx.dtype)
+
+    def forward(self, x, batch, cache, state, pending=None):
+        if isinstance(pending, ops.Pending):
+            pending.finish()
+        h = self._rows(x, pending)
+        if hasattr(self.mixer, "forward_pair"):
+            h = self._close(x, self.mixer_norm, pair=self.mixer.forward_pair(h, batch, cache, state))
+        else:
+            y = torch.zeros(x.shape, dtype=torch.float32, device=x.device)
+            left = self.mixer.forward(h, y, batch, cache, state)
+            if isinstance(left, ops.Pending):
+                left.finish()
+            h = self._close(x, self.mixer_norm, y=y)
+        planes.record(batch, "after_mixer", x)
+        if self.has_ff:
+            y = torch.zeros(x.shape, dtype=torch.float32, device=x.device)
+            left = self.feed_forward.forward(x if h is None else h, y, batch)
+            if isinstance(left, ops.Pending):
+                left.finish()
+            h = self._close(x, self.feed_forward_norm, y=y)
+        planes.record(batch, "after_feed_forward", x)
+        return None if h is None or planes.dumping(batch) else RoundedRows(x, h)
+
+
 register_part("block", "pre_norm", PreNormBlock)
+register_part("block", "post_norm", PostNormBlock)
 register_part("block", "parallel", ParallelBlock)
 register_part("block", "pre_norm_scaled", ScaledPreNormBlock)
 register_part("block", "hyper_connections", HyperConnectionBlock)

@@ -1,6 +1,8 @@
 """Grouped-query attention over the paged cache with its mask, softmax and gate chosen by parameters.
 
     q, k, v = Wq h, Wk h, Wv h                         (heads x dim, kv_heads x dim, kv_heads x vdim; no biases)
+    with row_norm: q <- q / rms(q) * wq, k <- k / rms(k) * wk, each over its WHOLE row (all heads at once, before they are
+                   split into heads and before the rotation; eps inside the root; a weight per column)
     q, k rotated on their first `rot_dims` dimensions   (pairing "half": (i, i + rot_dims / 2); "interleaved": (2i, 2i + 1))
     q, k divided by their root mean square over dim     (with unit_norm; eps inside the root, no weight)
     score = q . k * scale over the keys the mask shows:
@@ -17,9 +19,10 @@ the layer the model's run order names. What the cache retains is given apart fro
 sizes of every layer that reads it; empty: everything), because the layers that share a cache may look back differently
 far. Rotation angles, the unit norm, scores, softmax and the gate are 32-bit; q, k, v are rounded once.
 
-params: hidden_size, heads, kv_heads, dim, vdim, scale, eps, rot_dims, rot_base, pairing, unit_norm, mask, window,
-keep_first, chunk, sink, gate, reads_cache, cache_chunks, cache_keep_all (a window's cache keeps everything: a reader
-looks back further), and the tensor names q, k, v, g, o, sink (`<key>_name`).
+params: hidden_size, heads, kv_heads, dim, vdim, scale, eps, rot_dims, rot_base, rot_scaling (ops.rope_frequencies),
+pairing, unit_norm, row_norm, mask, window, keep_first, chunk, sink, gate, reads_cache, cache_chunks, cache_keep_all (a
+window's cache keeps everything: a reader looks back further), and the tensor names q, k, v, g, o, sink, q_norm, k_norm
+(`<key>_name`).
 """
 from __future__ import annotations
 
@@ -31,7 +34,8 @@ from ..weights import ParamSpec
 from . import planes
 from .registry import CacheNeed, Mixer, register_part, to_compute
 
-_DEFAULT_NAMES = dict(q="mix.q", k="mix.k", v="mix.v", g="mix.g", o="mix.o", sink="mix.sink")
+_DEFAULT_NAMES = dict(q="mix.q", k="mix.k", v="mix.v", g="mix.g", o="mix.o", sink="mix.sink", q_norm="mix.q.norm",
+                      k_norm="mix.k.norm")
 
 
 def _chunks_dead(spec, q):
@@ -59,7 +63,7 @@ class MaskedAttentionMixer(Mixer):
         self.pairing = p.get("pairing", "half")
         if self.rot_dims % 2 or self.rot_dims > self.dim or self.pairing not in ops.PAIRINGS:
             raise ValueError(f"attention: {self.rot_dims} rotated dimensions ({self.pairing!r}) of a head of {self.dim}")
-        self.unit_norm = bool(p.get("unit_norm", False))
+        self.unit_norm, self.row_norm = bool(p.get("unit_norm", False)), bool(p.get("row_norm", False))
         self.mask = p.get("mask") or "causal"
         if self.mask not in ops.MASKS:
             raise ValueError(f"attention: mask {self.mask!r} is not known (known: {sorted(ops.MASKS)})")
@@ -76,9 +80,9 @@ class MaskedAttentionMixer(Mixer):
         if self.mask != "chunk" and self.cache_chunks:
             raise ValueError("attention: the cache retains less than the mask sees")
         self.names = {k: prefix + p.get(k + "_name", d) for k, d in _DEFAULT_NAMES.items()}
-        self.w_in = self.wo = self.sink = self.table = None
+        self.w_in = self.wo = self.sink = self.table = self.row_norm_w = None
         if not ctx.is_meta:
-            self.table = ops.shared_rope_table(self.rot_dims, self.rot_base, ctx.max_model_len, ctx.device)
+            self.table = ops.shared_rope_table(self.rot_dims, self.rot_base, ctx.max_model_len, ctx.device, p.get("rot_scaling"))
 
     @property
     def n_q(self):
@@ -97,6 +101,10 @@ class MaskedAttentionMixer(Mixer):
         specs = [ParamSpec(n["q"], (self.n_q, W))]
         if not self.reads_cache:
             specs += [ParamSpec(n["k"], (self.kv_heads * self.dim, W)), ParamSpec(n["v"], (self.kv_heads * self.vdim, W))]
+        if self.row_norm:
+            specs.append(ParamSpec(n["q_norm"], (self.n_q,), init="ones"))
+            if not self.reads_cache:
+                specs.append(ParamSpec(n["k_norm"], (self.kv_heads * self.dim,), init="ones"))
         if self.has_sink:
             specs.append(ParamSpec(n["sink"], (self.heads,), init="zeros"))
         if self.n_gate:
@@ -111,6 +119,9 @@ class MaskedAttentionMixer(Mixer):
         self.w_in = ops.Weight(torch.cat([m.to(dt) for m in mats], 0).contiguous())     # rows [q | k | v | g] or [q | g]
         self.wo = ops.Weight(t["o"])
         self.sink = t["sink"].to(torch.float32).contiguous() if self.has_sink else None
+        if self.row_norm:
+            wq = t["q_norm"].to(torch.float32).contiguous()
+            self.row_norm_w = (wq, wq if self.reads_cache else t["k_norm"].to(torch.float32).contiguous())
 
     def weight_bytes(self):
         return self.w_in.nbytes + self.wo.nbytes
@@ -132,7 +143,7 @@ class MaskedAttentionMixer(Mixer):
         ops.rope_norm_store(proj, (0, self.n_q, self.n_q + self.kv_heads * self.dim), batch.positions,
                             batch.slot_maps[cache.group] if write else None, self.table, self.rot_dims, self.pairing,
                             self.unit_norm, self.eps, q, cache.k, cache.v, self.heads, self.kv_heads, self.dim, self.vdim,
-                            self.ctx.page_size)
+                            self.ctx.page_size, row_norm=self.row_norm_w, row_norm_eps=self.eps)
         att = torch.empty(T, self.heads * self.vdim, dtype=self.ctx.dtype, device=xn.device)
         ops.attention_masked(q, cache.k, cache.v, batch, cache.group, att, self.heads, self.kv_heads, self.dim, self.vdim,
                              self.ctx.page_size, self.scale, self.mask, self.window, self.keep_first, self.chunk, self.sink,

@@ -11,18 +11,24 @@ from .registry import Part, register_part, to_compute
 
 
 class RMSNorm(Part):
-    """params: name (tensor name relative to the prefix), size, eps."""
+    """params: name (tensor name relative to the prefix), size, eps, one_plus (default False: the weight multiplies as it is
+    stored; True: the tensor is stored around zero and the row is multiplied by 1 + w, a sum made in 32-bit at load and kept
+    in 32-bit)."""
 
     def __init__(self, params, ctx, prefix=""):
         super().__init__(params, ctx, prefix)
         self.size, self.eps = int(params["size"]), float(params["eps"])
         self.name = prefix + params["name"]
+        self.one_plus = bool(params.get("one_plus", False))
         self.weight = None
 
     def param_specs(self):
-        return [ParamSpec(self.name, (self.size,), init="ones")]
+        return [ParamSpec(self.name, (self.size,), init="zeros" if self.one_plus else "ones")]
 
     def load(self, tensors):
+        if self.one_plus:
+            self.weight = (tensors[self.name].to(torch.float32) + 1.0).contiguous()
+            return
         self.weight = to_compute(tensors[self.name], self.ctx)
 
     def weight_bytes(self):

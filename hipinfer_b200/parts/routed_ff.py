@@ -6,13 +6,18 @@ runs `top`.
     out = sum over the chosen e of Wdown_e (silu(Wgate_e v) * (Wup_e v)),  v = s_e h     the score multiplies the INPUT
 
 Without biases Wgate_e (s h) = s (Wgate_e h): the products run on h and the score enters the activation in 32-bit.
+
+A second form is chosen by parameters: `router_bias` adds a bias to the router's logits; `score` "softmax_chosen" lets the
+`top` largest LOGITS choose and takes as weights the softmax over the chosen logits alone; `weight_at` "output" multiplies
+the expert's RESULT by the weight (brought in at the activation too: the down product is linear).
 Steps of single rows (decoding) run on the device alone (csrc/moe.cu), so they replay from a CUDA graph: a few rows one
 by one, more of them sorted by expert so that an expert's weights are read once for all of its rows. A step with prompt
 portions sorts its (row, choice) pairs by expert and gives each expert's block of rows to the ordinary products (the
 tensor-core kernels in bfloat16), for which the host reads the experts' row counts once a layer.
 
-params: hidden_size, experts, top, expert_size, router_name (default "mlp.router"), expert_prefix (default "mlp.e": expert
-i's tensors are <expert_prefix><i>.gate / .up / .down).
+params: hidden_size, experts, top, expert_size, score (default "sigmoid"), weight_at (default "input"), router_bias
+(default False), router_name (default "mlp.router"), router_bias_name (default "mlp.router.b"), expert_prefix (default
+"mlp.e": expert i's tensors are <expert_prefix><i>.gate / .up / .down).
 """
 from __future__ import annotations
 
@@ -34,7 +39,14 @@ class RoutedFF(Part):
         self.inter = int(params["expert_size"])
         if not 1 <= self.top <= self.experts:
             raise ValueError(f"routed feed-forward: top {self.top} of {self.experts} experts")
+        self.score, self.weight_at = params.get("score", "sigmoid"), params.get("weight_at", "input")
+        if self.score not in ops.MOE_SCORES or self.weight_at not in ("input", "output"):
+            raise ValueError(f"routed feed-forward: score {self.score!r} (known: {sorted(ops.MOE_SCORES)}), weight_at "
+                             f"{self.weight_at!r} (known: 'input', 'output')")
+        self.at_output = self.weight_at == "output"
         self.router_name = prefix + params.get("router_name", "mlp.router")
+        self.router_bias_name = prefix + params.get("router_bias_name", "mlp.router.b") if params.get("router_bias") else None
+        self.router_bias = None
         self.expert_prefix = prefix + params.get("expert_prefix", "mlp.e")
         self.router = self.wgu = self.wdown = None
 
@@ -43,6 +55,8 @@ class RoutedFF(Part):
 
     def param_specs(self):
         specs = [ParamSpec(self.router_name, (self.experts, self.hidden))]
+        if self.router_bias_name:
+            specs.append(ParamSpec(self.router_bias_name, (self.experts,), init="zeros"))
         for i in range(self.experts):
             specs += [ParamSpec(self._expert(i, "gate"), (self.inter, self.hidden)),
                       ParamSpec(self._expert(i, "up"), (self.inter, self.hidden)),
@@ -52,6 +66,8 @@ class RoutedFF(Part):
     def load(self, tensors):
         t = lambda name: to_compute(tensors[name], self.ctx)
         self.router = t(self.router_name)
+        if self.router_bias_name:
+            self.router_bias = t(self.router_bias_name).to(self.router.dtype).contiguous()
         mats = [t(self._expert(i, k)) for i in range(self.experts) for k in ("gate", "up", "down")]
         dt = mats[0].dtype if all(m.dtype == mats[0].dtype for m in mats) else torch.float32
         E, F, W = self.experts, self.inter, self.hidden
@@ -68,16 +84,16 @@ class RoutedFF(Part):
 
     def forward(self, xn, x, batch):
         T, top, F = xn.shape[0], self.top, self.inter
-        expert, score = ops.moe_route(xn, self.router, top)
+        expert, score = ops.moe_route(xn, self.router, top, self.router_bias, self.score)
         if T * top < GROUPED_MIN_PAIRS:
-            ops.moe_rows(xn, self.wgu, self.wdown, expert, score, x)
+            ops.moe_rows(xn, self.wgu, self.wdown, expert, score, x, self.at_output)
             return None
         offsets, pos, src = ops.moe_sort(expert, self.experts)
         if getattr(batch, "max_q_len", 1) <= 1 or T * top < SORTED_MIN_PAIRS:
             gu = torch.empty(T * top, 2 * F, dtype=torch.float32, device=xn.device)
             ops.moe_grouped(xn, src, top, self.wgu, offsets, gu)
             act = torch.empty(T * top, F, dtype=self.ctx.dtype, device=xn.device)
-            ops.moe_act(gu, src, score, act)
+            ops.moe_act(gu, src, score, act, self.at_output)
             planes.record(batch, "activation", act)
             ys = torch.empty(T * top, self.hidden, dtype=torch.float32, device=xn.device)
             ops.moe_grouped(act, None, 1, self.wdown, offsets, ys)
@@ -91,7 +107,7 @@ class RoutedFF(Part):
             if hi > lo:
                 ops.linear(xs[lo:hi], self.w_gu_e[e], gu[lo:hi])
         act = torch.empty(T * top, F, dtype=self.ctx.dtype, device=xn.device)
-        ops.moe_act(gu, src, score, act)
+        ops.moe_act(gu, src, score, act, self.at_output)
         planes.record(batch, "activation", act)
         ys = torch.empty(T * top, self.hidden, dtype=torch.float32, device=xn.device)
         for e in range(self.experts):
