@@ -518,8 +518,34 @@ def runopel_configs(size: dict, window: int):
     return runopel, vegodra_configs(size, window)[0]
 
 
-DESIGNS = {"torirax": design_configs, "vegodra": vegodra_configs, "runopel": runopel_configs}
-BESIDE = {"torirax": "llama", "vegodra": "llama", "runopel": "vegodra"}
+def mavinex_configs(size: dict, window: int):
+    """(Mavinex config, Runopel config) of equal width, depth, head counts and feed-forward width; Runopel is the closest
+    of the other designs (latent attention with a sliding window, a state-space mixer, experts). Mavinex's layers stand
+    where Runopel's like layers stand: latent attention (a sink, a gate per head, YaRN) at 0 and 2 of every four; at 1
+    and 3 grouped-query attention with a sliding window beside the selective state-space mixer (heads x head_dim
+    channels, 16 states a channel, a step-size rank of width / 16, four taps). Every layer has eight experts of half the
+    dense width, two per token (as many active weights as the dense feed-forward). The norm comes after the sum."""
+    W, L, H, G, D = size["width"], size["layers"], size["heads"], size["kv"], size["head_dim"]
+    layers = []
+    mlp = dict(kind="moe", expert=dict(ff=size["ff"] // 2), router=dict(experts=8, top=2))
+    for i in range(L):
+        if i % 4 in (0, 2):
+            m = dict(heads=H, dim=D, rot_dim=D // 2, vdim=D, kv_rank=4 * D, scale=(D + D // 2) ** -0.5,
+                     rot=dict(base=10000.0, dims=D // 2, scaling=dict(factor=4.0, original=CONTEXT_LEN // 4, fast=32.0, slow=1.0)),
+                     mask=dict(size=window))
+            layers.append(dict(type="latent_attention", mixer=m, mlp=mlp))
+        else:
+            left = dict(heads=H, kv_heads=G, dim=D, vdim=D, scale=D ** -0.5, mask=dict(size=window),
+                        rot=dict(base=500000.0, dims=D, scaling=dict(factor=8.0, low=1.0, high=4.0, original=CONTEXT_LEN // 4)))
+            right = dict(inner=H * D, state=16, dt_rank=W // 16, conv=4)
+            layers.append(dict(type="parallel", mixer=dict(left=left, right=right), mlp=mlp))
+    mavinex = dict(architecture="Mavinex", vocab=size["vocab"], width=W, max_positions=CONTEXT_LEN, norm=dict(eps=1e-5),
+                   postln_alpha=2.0, embedding=dict(scale=1.0), layers=layers)
+    return mavinex, runopel_configs(size, window)[0]
+
+
+DESIGNS = {"torirax": design_configs, "vegodra": vegodra_configs, "runopel": runopel_configs, "mavinex": mavinex_configs}
+BESIDE = {"torirax": "llama", "vegodra": "llama", "runopel": "vegodra", "mavinex": "runopel"}
 
 
 def kernel_table(one, reps: int = 3):
@@ -564,7 +590,7 @@ def kernel_table(one, reps: int = 3):
 
 def design_bench(a) -> int:
     """Prefill and decode throughput of the chosen design and of the model beside it (the Llama decoder for Torirax and
-    Vegodra, Vegodra for Runopel) at equal layer sizes, with each step's kernels by name; one JSON line. The default run
+    Vegodra, Vegodra for Runopel, Runopel for Mavinex) at equal layer sizes, with each step's kernels by name; one JSON line. The default run
     of this file is untouched by this option."""
     import torch
 
@@ -715,7 +741,7 @@ def main() -> int:
                     help="prefill and decode of this design beside its closest other model at equal layer sizes (see --sizes); "
                          "the default run is not changed by it")
     ap.add_argument("--sizes", default="1b", help="with --design: layer sizes, of " + ", ".join(sorted(DESIGN_SIZES)) + " (commas between)")
-    ap.add_argument("--window", type=int, default=1024, help="with --design: the attention window (torirax: the first 4 tokens are kept; runopel) or chunk size (vegodra)")
+    ap.add_argument("--window", type=int, default=1024, help="with --design: the attention window (torirax: the first 4 tokens are kept; runopel; mavinex) or chunk size (vegodra)")
     a = ap.parse_args()
     if a.impl == "reference":
         return reference_arm(a)

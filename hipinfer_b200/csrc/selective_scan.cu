@@ -14,6 +14,10 @@
 // finished in place, the chunk's results leave through shared memory in whole rows. Requests, lengths and state slots come
 // from device arrays, so a decode-only step replays from a CUDA graph; a token's arithmetic does not depend on where a
 // portion or a chunk starts.
+//   Long portions run in three launches over pieces of L tokens instead, so that one long prompt fills the GPU: every piece
+// from a zero state (what it adds itself, and the sum of its step sizes, whose exponential times the rate is the product
+// of its decays), then the pieces' starting states one after another (selective_carry_kernel), then every piece again from
+// its starting state for the results. The walk is the same code in all three; the two ways differ by rounding only.
 #include "common.cuh"
 
 constexpr int SEL_CH = 16;         // tokens a chunk
@@ -38,10 +42,22 @@ struct SelArgs {
   const int* q_start; const int* q_len; const int* slot;
   void* out; long ldo;               // [T][inner]
   int inner, N, KS;
+  int L;                             // tokens a piece (the three-launch form)
+  float* piece_state;                // [all requests' pieces][inner][N]
+  float* piece_dt;                   // [all requests' pieces][inner]: the sum of a piece's step sizes
 };
 
+enum { SEL_WHOLE = 0, SEL_PIECE_LOCAL = 1, SEL_PIECE_OUT = 2 };
+
+// The first piece of request r among all requests' pieces: every request before it has ceil(len / L) of them.
+__device__ __forceinline__ int sel_piece_base(const int* q_len, int r, int L) {
+  int base = 0;
+  for (int i = 0; i < r; i++) base += (q_len[i] + L - 1) / L;
+  return base;
+}
+
 // shared memory of a block: two buffers of a chunk's rows, each [SEL_CH][2N + 3 CPB]: B | C | dt | x | z (z becomes the result)
-template <typename TW, typename TO, int NPT>
+template <typename TW, typename TO, int NPT, int MODE>
 __global__ void __launch_bounds__(SEL_THREADS) selective_scan_kernel(SelArgs A) {
   extern __shared__ float sel_sm[];
   hb_pdl_launch();
@@ -62,13 +78,26 @@ __global__ void __launch_bounds__(SEL_THREADS) selective_scan_kernel(SelArgs A) 
   }
   const float dskip = live ? hb_to_float(((const TW*)A.d_skip)[c]) : 0.f;
   hb_pdl_wait();
-  const int len = A.q_len[r], t0 = A.q_start[r];
-  if (len <= 0) return;
-  float* st = A.state + ((size_t)A.slot[r] * A.inner + (live ? c : 0)) * N;
+  int len = A.q_len[r], t0 = A.q_start[r];
+  float* st;
+  size_t piece = 0;
+  if (MODE == SEL_WHOLE) {
+    if (len <= 0) return;
+    st = A.state + ((size_t)A.slot[r] * A.inner + (live ? c : 0)) * N;
+  } else {
+    // this block's piece: tokens [z L, z L + L) of the request, the walk below sees them as a portion of their own
+    const int j_first = blockIdx.z * A.L;
+    if (j_first >= len) return;
+    piece = (size_t)sel_piece_base(A.q_len, r, A.L) + blockIdx.z;
+    st = A.piece_state + (piece * A.inner + (live ? c : 0)) * N;
+    t0 += j_first;
+    len = min(A.L, len - j_first);
+  }
+  float sum_dt = 0.f;
 #pragma unroll
   for (int i = 0; i < NPT; i++) {
     const int n = ks + i * KS;
-    S[i] = (live && n < N) ? st[n] : 0.f;
+    S[i] = (MODE != SEL_PIECE_LOCAL && live && n < N) ? st[n] : 0.f;
   }
   auto fetch = [&](int j0, float* b) {
     const int n = min(SEL_CH, len - j0);
@@ -110,30 +139,36 @@ __global__ void __launch_bounds__(SEL_THREADS) selective_scan_kernel(SelArgs A) 
       const float* row = b + j * row_w;
       const float dtv = row[2 * N + cl], xv = row[2 * N + CPB + cl];
       const float dx = dtv * xv;
+      if (MODE == SEL_PIECE_LOCAL) sum_dt += dtv;
       float acc = 0.f;
 #pragma unroll
       for (int i = 0; i < NPT; i++) {
         const int n = ks + i * KS;
         if (n < N) {
           S[i] = fmaf(expf(dtv * rate[i]), S[i], dx * row[n]);
-          acc = fmaf(S[i], row[N + n], acc);
+          if (MODE != SEL_PIECE_LOCAL) acc = fmaf(S[i], row[N + n], acc);
         }
       }
-      for (int o = KS >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-      if (ks == 0) {
-        const float zz = row[2 * N + 2 * CPB + cl];
-        b[j * row_w + 2 * N + 2 * CPB + cl] = fmaf(dskip, xv, acc) * (zz / (1.f + expf(-zz)));
+      if (MODE != SEL_PIECE_LOCAL) {
+        for (int o = KS >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (ks == 0) {
+          const float zz = row[2 * N + 2 * CPB + cl];
+          b[j * row_w + 2 * N + 2 * CPB + cl] = fmaf(dskip, xv, acc) * (zz / (1.f + expf(-zz)));
+        }
       }
     }
     __syncthreads();
-    TO* out = (TO*)A.out;
-    for (int i = threadIdx.x; i < n_tok * nch; i += SEL_THREADS) {
-      const int j = i / nch, k = i - j * nch;
-      out[(size_t)(t0 + j0 + j) * A.ldo + c0 + k] = hb_from_float<TO>(b[j * row_w + 2 * N + 2 * CPB + k]);
+    if (MODE != SEL_PIECE_LOCAL) {
+      TO* out = (TO*)A.out;
+      for (int i = threadIdx.x; i < n_tok * nch; i += SEL_THREADS) {
+        const int j = i / nch, k = i - j * nch;
+        out[(size_t)(t0 + j0 + j) * A.ldo + c0 + k] = hb_from_float<TO>(b[j * row_w + 2 * N + 2 * CPB + k]);
+      }
+      __syncthreads();     // the buffer is asked for again two chunks on
     }
-    __syncthreads();     // the buffer is asked for again two chunks on
   }
-  if (live) {
+  if (MODE == SEL_PIECE_LOCAL && live && ks == 0) A.piece_dt[piece * A.inner + c] = sum_dt;
+  if (MODE != SEL_PIECE_OUT && live) {
 #pragma unroll
     for (int i = 0; i < NPT; i++) {
       const int n = ks + i * KS;
@@ -142,32 +177,90 @@ __global__ void __launch_bounds__(SEL_THREADS) selective_scan_kernel(SelArgs A) 
   }
 }
 
+// The pieces' starting states, one after another: an element (channel, state) of a request walks its pieces, leaves in each
+// the state the piece starts from and carries exp(rate * the piece's summed step sizes) * state + the piece's own
+// contribution on; the last goes to the request's slot.
+template <typename TW>
+__global__ void __launch_bounds__(256) selective_carry_kernel(SelArgs A) {
+  hb_pdl_launch();
+  hb_pdl_wait();
+  const int r = blockIdx.y, N = A.N;
+  const size_t e = (size_t)blockIdx.x * 256 + threadIdx.x, IN = (size_t)A.inner * N;
+  if (e >= IN) return;
+  const int len = A.q_len[r];
+  if (len <= 0) return;
+  const int c = (int)(e / N), pieces = (len + A.L - 1) / A.L;
+  const float rate = -expf(hb_to_float(((const TW*)A.a_log)[e]));
+  float* slot = A.state + (size_t)A.slot[r] * IN + e;
+  float carry = *slot;
+  const size_t base = (size_t)sel_piece_base(A.q_len, r, A.L);
+  float* ps = A.piece_state + base * IN + e;
+  const float* pd = A.piece_dt + base * A.inner + c;
+  for (int k0 = 0; k0 < pieces; k0 += 8) {                 // eight pieces' loads in flight, then their chain
+    float own[8], dec[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      const bool in = k0 + i < pieces;
+      own[i] = in ? ps[(size_t)(k0 + i) * IN] : 0.f;
+      dec[i] = in ? expf(rate * pd[(size_t)(k0 + i) * A.inner]) : 1.f;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      if (k0 + i < pieces) {
+        ps[(size_t)(k0 + i) * IN] = carry;
+        carry = fmaf(dec[i], carry, own[i]);
+      }
+    }
+  }
+  *slot = carry;
+}
+
 // x, dt, z float32 [T][inner] (row strides ldx, lddt, ldz), bc float32 rows of B [N] | C [N] (stride ldbc); dt_bias [inner],
 // a_log [inner][N], d_skip [inner] in the element type w_dt; state float32 [slots][inner][N]; out [T][inner] in o_dt.
+// pieces > 0: the three-launch form over pieces of piece_len tokens, no request with more than `pieces` of them, with room
+// for all requests' pieces (at most rows / piece_len + n_requests) in piece_state [.][inner][N] and piece_dt [.][inner].
 HB_EXPORT int hb_selective_scan(const float* x, long ldx, const float* dt, long lddt, const float* bc, long ldbc, const float* z,
                                 long ldz, const void* dt_bias, const void* a_log, const void* d_skip, int w_dt, float* state,
                                 const int* q_start, const int* q_len, const int* slot, void* out, int o_dt, long ldo,
-                                int n_requests, int inner, int N, cudaStream_t s) {
+                                int n_requests, int inner, int N, int piece_len, int pieces, float* piece_state,
+                                float* piece_dt, cudaStream_t s) {
   if (n_requests <= 0 || inner <= 0) return 0;
+  if (pieces > 0 && (piece_len <= 0 || !piece_state || !piece_dt || pieces > 65535)) HB_FAIL("hb_selective_scan: %d pieces of %d", pieces, piece_len);
   if (N < 1 || N > 256) HB_FAIL("hb_selective_scan: %d states a channel (1 to 256 are supported)", N);
   int KS = 1;
   while (KS < 32 && (N + KS - 1) / KS > 4) KS <<= 1;
   const int npt = (N + KS - 1) / KS, CPB = SEL_THREADS / KS;
-  SelArgs A = {x, ldx, dt, lddt, bc, ldbc, z, ldz, dt_bias, a_log, d_skip, state, q_start, q_len, slot, out, ldo, inner, N, KS};
-  dim3 grid((inner + CPB - 1) / CPB, n_requests);
+  SelArgs A = {x, ldx, dt, lddt, bc, ldbc, z, ldz, dt_bias, a_log, d_skip, state, q_start, q_len, slot, out, ldo, inner, N, KS,
+               piece_len, piece_state, piece_dt};
+  dim3 grid((inner + CPB - 1) / CPB, n_requests, pieces > 0 ? pieces : 1);
   if (grid.y > 65535) HB_FAIL("hb_selective_scan: the grid is too large");
   const size_t smem = (size_t)2 * SEL_CH * (2 * N + 3 * CPB) * sizeof(float);
-#define SEL_LAUNCH(NPT)                                                                                      \
+#define SEL_LAUNCH_MODE(NPT, MODE)                                                                           \
   HB_DISPATCH_2(w_dt, o_dt, "hb_selective_scan", do {                                                        \
-    auto kern = selective_scan_kernel<TA, TB, NPT>;                                                          \
+    auto kern = selective_scan_kernel<TA, TB, NPT, MODE>;                                                    \
     if (smem > 40 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
     hb_launch(kern, grid, dim3(SEL_THREADS), smem, s, A);                                                    \
   } while (0))
-  if (npt <= 1) SEL_LAUNCH(1);
-  else if (npt <= 2) SEL_LAUNCH(2);
-  else if (npt <= 4) SEL_LAUNCH(4);
-  else SEL_LAUNCH(8);
+#define SEL_LAUNCH(MODE)                     \
+  do {                                       \
+    if (npt <= 1) SEL_LAUNCH_MODE(1, MODE);  \
+    else if (npt <= 2) SEL_LAUNCH_MODE(2, MODE); \
+    else if (npt <= 4) SEL_LAUNCH_MODE(4, MODE); \
+    else SEL_LAUNCH_MODE(8, MODE);           \
+  } while (0)
+  if (pieces <= 0) {
+    SEL_LAUNCH(SEL_WHOLE);
+  } else {
+    SEL_LAUNCH(SEL_PIECE_LOCAL);
+    HB_CHECK_LAUNCH("hb_selective_scan");
+    const size_t elems = (size_t)inner * N;
+    HB_DISPATCH_1(w_dt, "hb_selective_scan",
+                  (hb_launch(selective_carry_kernel<TA>, dim3((unsigned)((elems + 255) / 256), n_requests), dim3(256), 0, s, A)));
+    HB_CHECK_LAUNCH("hb_selective_scan");
+    SEL_LAUNCH(SEL_PIECE_OUT);
+  }
 #undef SEL_LAUNCH
+#undef SEL_LAUNCH_MODE
   HB_CHECK_LAUNCH("hb_selective_scan");
   return 0;
 }

@@ -67,7 +67,8 @@ _SIGS = {
         "hb_ssd_conv": [_p, _l, _i, _p, _p, _i, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p],
         "hb_ssd_scan": [_p, _l, _p, _l, _p, _p, _p, _i, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _p, _p],
         "hb_ssd_gate_norm": [_p, _p, _l, _p, _i, _p, _i, _i, _i, _i, _f, _p],
-        "hb_selective_scan": [_p, _l, _p, _l, _p, _l, _p, _l, _p, _p, _p, _i, _p, _p, _p, _p, _p, _i, _l, _i, _i, _i, _p],
+        "hb_selective_scan": [_p, _l, _p, _l, _p, _l, _p, _l, _p, _p, _p, _i, _p, _p, _p, _p, _p, _i, _l, _i, _i, _i, _i, _i, _p, _p,
+                              _p],
         "hb_residual_norm": [_p, _p, _p, _p, _p, _p, _i, _f, _f, _f, _p, _f, _p, _i, _i, _i, _p],
         "hb_moe_route": [_p, _i, _l, _p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _p],
         "hb_moe_gate_up_rows": [_p, _i, _l, _p, _i, _p, _p, _p, _i, _i, _i, _i, _i, _p],
@@ -1193,13 +1194,20 @@ def ssd_gate_norm(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, out: t
     return out
 
 
+SEL_PIECE_TOKENS = 64    # tokens a piece of the selective recurrence (selective_scan); 0: always one walk a request
+
+
 def selective_scan(x: torch.Tensor, dt: torch.Tensor, bc: torch.Tensor, z: torch.Tensor, dt_bias: torch.Tensor,
                    a_log: torch.Tensor, d_skip: torch.Tensor, state: torch.Tensor, batch, out: torch.Tensor) -> torch.Tensor:
     """The selective recurrence with a decay per (channel, state) pair over the step's rows, request by request, from and
     into each request's state slot (csrc/selective_scan.cu). x, dt, z float32 [T, inner] (views of wider rows are fine):
     the convolved input, the step-size product without its bias, the gate's pre-activation; bc float32 [T, 2N]: B then C;
     dt_bias [inner], a_log [inner, N], d_skip [inner]; state float32 [slots, inner, N]. out [T, inner] = (sum_n S C + D x)
-    silu(z), rounded once."""
+    silu(z), rounded once.
+
+    A step whose longest portion has at least three times SEL_PIECE_TOKENS rows runs in pieces of that many tokens (every
+    piece from a zero state, the pieces' starting states one after another, every piece again for the results), so that a
+    long prompt fills the GPU; the results differ from the walk in one go by rounding only."""
     _need_cuda(x, dt, bc, z, dt_bias, a_log, d_skip, state, out)
     for t, what in ((x, "x"), (dt, "dt"), (bc, "bc"), (z, "z"), (out, "out")):
         _rows_contiguous(t, "selective_scan " + what)
@@ -1209,10 +1217,16 @@ def selective_scan(x: torch.Tensor, dt: torch.Tensor, bc: torch.Tensor, z: torch
     assert dt.shape == z.shape == out.shape == (T, inner) and bc.shape == (T, 2 * N) and state.shape[1:] == (inner, N)
     assert a_log.is_contiguous() and a_log.shape[0] == inner and dt_bias.numel() == d_skip.numel() == inner
     assert dt_bias.dtype == a_log.dtype == d_skip.dtype
+    L, pieces, piece_state, piece_dt = int(SEL_PIECE_TOKENS), 0, None, None
+    if L > 0 and batch.max_q_len >= 3 * L:
+        pieces = -(-batch.max_q_len // L)
+        room = T // L + batch.n_requests               # all requests' pieces: every request ends with at most one short piece
+        piece_state = torch.empty(room, inner, N, dtype=torch.float32, device=x.device)
+        piece_dt = torch.empty(room, inner, dtype=torch.float32, device=x.device)
     _call("hybrid", "hb_selective_scan", x.data_ptr(), x.stride(0), dt.data_ptr(), dt.stride(0), bc.data_ptr(), bc.stride(0),
           z.data_ptr(), z.stride(0), dt_bias.data_ptr(), a_log.data_ptr(), d_skip.data_ptr(), _dt(a_log), state.data_ptr(),
           batch.req_q_start.data_ptr(), batch.req_q_len.data_ptr(), batch.req_state_slot.data_ptr(), out.data_ptr(), _dt(out),
-          out.stride(0), batch.n_requests, inner, N, _stream())
+          out.stride(0), batch.n_requests, inner, N, L, pieces, _ptr(piece_state), _ptr(piece_dt), _stream())
     return out
 
 

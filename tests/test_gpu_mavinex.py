@@ -75,6 +75,17 @@ def test_whole_prompts(setup):
     _check(setup, tiny.plan_whole(setup["requests"]), "whole")
 
 
+def test_whole_prompts_with_the_recurrence_in_short_pieces(setup, monkeypatch):
+    """Prompts of a few dozen tokens already run the selective recurrence in pieces (of 8 tokens), in a batch of unequal
+    requests too; the states the pieces leave are the ones that the single tokens after them start from."""
+    from hipinfer_b200.kernels import ops
+
+    monkeypatch.setattr(ops, "SEL_PIECE_TOKENS", 8)
+    _check(setup, tiny.plan_whole(setup["requests"]), "whole in pieces")
+    _check(setup, tiny.plan_tail_decode(setup["requests"], 5), "pieces then single tokens")
+    _check(setup, tiny.plan_mixed(setup["requests"], 11), "mixed in pieces")
+
+
 def test_last_tokens_one_by_one(setup):
     _check(setup, tiny.plan_tail_decode(setup["requests"], 48), "tail")
 

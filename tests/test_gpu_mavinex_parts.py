@@ -217,6 +217,46 @@ def test_selective_recurrence_is_the_same_however_the_tokens_are_cut(dtype):
         assert torch.equal(got, whole) and torch.equal(s0, s1)
 
 
+@pytest.mark.parametrize("I,N", [(48, 8), (18, 7), (96, 16), (40, 200)])
+@pytest.mark.parametrize("piece", [4, 16, 64])
+def test_selective_recurrence_in_pieces(I, N, piece, monkeypatch):
+    """Portions long enough run in pieces (every piece from a zero state, the starting states in order, every piece again
+    for the results): unequal requests, one that ends inside a piece, one of a single token, states that an earlier portion
+    left; against the plain scan and against the walk in one go. The states the pieces leave are those the next tokens
+    start from."""
+    from hipinfer_b200.kernels import ops
+
+    lens, then = [3 * piece + 5, 1, 4 * piece, 3 * piece - 1], 3 * piece + 2
+    ins = [_scan_inputs(n + then + 2, I, N, 10 * r) for r, n in enumerate(lens)]
+    a_log, dt_bias, d = ins[0][4], ins[0][5], ins[0][6]
+    want = [_scan_plain(x, dr, bc, z, a_log, dt_bias, d, N) for x, dr, bc, z, *_ in ins]
+    consts = [t.to(DEV) for t in (dt_bias, a_log, d)]
+    slots = [2, 0, 3, 1]
+
+    def run(piece_tokens):
+        monkeypatch.setattr(ops, "SEL_PIECE_TOKENS", piece_tokens)
+        state = torch.zeros(4, I, N, dtype=torch.float32, device=DEV)
+        outs, lo = [], [0] * 4
+        for ns in (lens, [then] * 4, [1] * 4, [1] * 4):
+            cat = lambda k: torch.cat([ins[r][k][lo[r]:lo[r] + ns[r]] for r in range(4)]).to(DEV)
+            out = torch.empty(sum(ns), I, dtype=torch.float32, device=DEV)
+            ops.selective_scan(cat(0), cat(1), cat(2), cat(3), *consts, state, batch_of(ns, slots=slots), out)
+            outs.append(out.cpu())
+            lo = [a + b for a, b in zip(lo, ns)]
+        return outs, state.cpu()
+
+    (got, state), (whole, state_w) = run(piece), run(0)
+    lo = [0] * 4
+    for k, ns in enumerate((lens, [then] * 4, [1] * 4, [1] * 4)):
+        o = 0
+        for r in range(4):
+            close(got[k][o:o + ns[r]], want[r][lo[r]:lo[r] + ns[r]], torch.float32, f"step {k}, request {r}", tol=1e-4)
+            close(got[k][o:o + ns[r]], whole[k][o:o + ns[r]], torch.float32, f"step {k}, request {r}: pieces against one walk", tol=1e-4)
+            o += ns[r]
+        lo = [a + b for a, b in zip(lo, ns)]
+    close(state, state_w, torch.float32, "the states left", tol=1e-4)
+
+
 def test_a_slow_decay_carries_a_far_token_and_a_fast_one_forgets_it():
     """Channel 0 decays by exp(-e^-9 dt) a token: what token 0 wrote is still there 600 tokens on. Channel 1 decays by
     exp(-e^3 dt): it holds the last token alone. The inputs of all tokens between are zero, so the result names the token."""
