@@ -636,7 +636,8 @@ __global__ void __launch_bounds__(256) rope_norm_store_kernel(const float* __res
       fk = rsqrtf(hb_block_sum(sk, red) / (float)(G * D) + pre_eps);
     }
   }
-  for (int hh = warp; hh < n_heads; hh += 8) {
+  // with few rows the heads of a row are split over gridDim.y blocks (each makes the row's sums for itself)
+  for (int hh = blockIdx.y * 8 + warp; hh < n_heads; hh += 8 * gridDim.y) {
     const float* src = hh < H ? row + q_off + (size_t)hh * D : row + k_off + (size_t)(hh - H) * D;
     if (pre_wq) {
       const TW* pw = hh < H ? pre_wq + (size_t)hh * D : pre_wk + (size_t)(hh - H) * D;
@@ -666,7 +667,7 @@ __global__ void __launch_bounds__(256) rope_norm_store_kernel(const float* __res
     __syncwarp();
   }
   if (slot < 0) return;
-  for (int i = threadIdx.x; i < G * E; i += 256) {
+  for (int i = blockIdx.y * 256 + threadIdx.x; i < G * E; i += 256 * gridDim.y) {
     const int h = i / E, e = i - h * E;
     vc[((page * G + h) * page_size + off) * E + e] = hb_from_float<TQ>(row[v_off + i]);
   }
@@ -683,8 +684,16 @@ HB_EXPORT int hb_rope_norm_store(const float* proj, long ld, int q_off, int k_of
   if (smem > 48 * 1024) HB_FAIL("hb_rope_norm_store: heads of %d are too wide", D);
   if ((pre_wq != nullptr) != (pre_wk != nullptr)) HB_FAIL("hb_rope_norm_store: a row norm needs the weights of q and of k");
   if (!pre_wq) pre_dt = q_dt;
+  // few rows: up to 8 blocks a row, so that a decode step's rows still spread over the machine
+  int split = 1;
+  if (T < 592) {
+    const int groups = (H + G + 7) / 8, want = 1184 / T;
+    split = groups < want ? groups : want;
+    if (split > 8) split = 8;
+    if (split < 1) split = 1;
+  }
   HB_DISPATCH_2(q_dt, pre_dt, "hb_rope_norm_store",
-                (hb_launch(rope_norm_store_kernel<TA, TB>, T, 256, smem, s, proj, ld, q_off, k_off, v_off, pos, slot_map,
+                (hb_launch(rope_norm_store_kernel<TA, TB>, dim3(T, split), 256, smem, s, proj, ld, q_off, k_off, v_off, pos, slot_map,
                            (const float2*)table, rot, rot_off, pairing, unit_norm, eps, (TA*)q_out, (TA*)kc, (TA*)vc, H, G, D, E,
                            page_size, (const TB*)pre_wq, (const TB*)pre_wk, pre_eps)));
   HB_CHECK_LAUNCH("hb_rope_norm_store");

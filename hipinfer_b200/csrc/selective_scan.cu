@@ -7,11 +7,11 @@
 //     dt = softplus(dt_raw + dt_bias_c);  A = -exp(A_log[c][n])
 //     S[c][n] <- exp(dt A) S[c][n] + (dt x_c) B_n;   y_c = sum_n S[c][n] C_n + D_c x_c;   out_c = y_c * silu(z_c)
 // The state S [inner][N] lives in 32-bit in the request's state slot and is carried from token to token and from step to
-// step; step sizes, decays, the exponentials and the sums are 32-bit (expf, log1pf; no fast-math), the result is rounded
-// once. A block owns (a tile of channels, a request) and walks the request's rows of the step in order: KS threads share a
+// step; step sizes, decays, the exponentials and the sums are 32-bit (expf, exp2f, log1pf; no fast-math), the result is
+// rounded once. A block owns (a tile of channels, a request) and walks the request's rows of the step in order: KS threads share a
 // channel, thread ks holds the states n = ks + i KS in registers, the KS partial sums of y are joined by shuffles. Tokens
 // go by in chunks of SEL_CH: a chunk's rows are asked for a chunk ahead (cp.async, two buffers), the step sizes are
-// finished in place, the chunk's results leave through shared memory in whole rows. Requests, lengths and state slots come
+// finished in place, the chunk's results leave through shared memory in whole rows, where the gate multiplies them. Requests, lengths and state slots come
 // from device arrays, so a decode-only step replays from a CUDA graph; a token's arithmetic does not depend on where a
 // portion or a chunk starts.
 //   Long portions run in three launches over pieces of L tokens instead, so that one long prompt fills the GPU: every piece
@@ -31,6 +31,9 @@ __device__ __forceinline__ void sel_commit() { asm volatile("cp.async.commit_gro
 template <int N> __device__ __forceinline__ void sel_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 __device__ __forceinline__ float sel_softplus(float v) { return fmaxf(v, 0.f) + log1pf(expf(-fabsf(v))); }
+// exp(dt * A) as 2^(dt * (A log2 e)): the rate comes multiplied by log2(e) once, a decay is one product and one exp2f
+__device__ __forceinline__ float sel_decay(float dt, float rate2) { return exp2f(dt * rate2); }
+constexpr float SEL_LOG2E = 1.4426950408889634f;
 
 struct SelArgs {
   const float* x; long ldx;          // [T][inner] after convolution and silu
@@ -74,7 +77,7 @@ __global__ void __launch_bounds__(SEL_THREADS) selective_scan_kernel(SelArgs A) 
 #pragma unroll
   for (int i = 0; i < NPT; i++) {
     const int n = ks + i * KS;
-    rate[i] = (live && n < N) ? -expf(hb_to_float(al[(size_t)c * N + n])) : 0.f;
+    rate[i] = (live && n < N) ? -expf(hb_to_float(al[(size_t)c * N + n])) * SEL_LOG2E : 0.f;
   }
   const float dskip = live ? hb_to_float(((const TW*)A.d_skip)[c]) : 0.f;
   hb_pdl_wait();
@@ -99,24 +102,67 @@ __global__ void __launch_bounds__(SEL_THREADS) selective_scan_kernel(SelArgs A) 
     const int n = ks + i * KS;
     S[i] = (MODE != SEL_PIECE_LOCAL && live && n < N) ? st[n] : 0.f;
   }
+  if (MODE == SEL_WHOLE && len == 1) {
+    // a single token (decoding): no staging; a thread asks for all it needs at once, beside its states above. The same
+    // operations in the same order as the walk below: the same bits.
+    const size_t t = (size_t)t0;
+    float dtr = 0.f, xv = 0.f, zz = 0.f, Bn[NPT], Cn[NPT];
+    if (live) {
+      dtr = A.dt[t * A.lddt + c];
+      xv = A.x[t * A.ldx + c];
+      zz = A.z[t * A.ldz + c];
+    }
+#pragma unroll
+    for (int i = 0; i < NPT; i++) {
+      const int n = ks + i * KS;
+      Bn[i] = n < N ? A.bc[t * A.ldbc + n] : 0.f;
+      Cn[i] = n < N ? A.bc[t * A.ldbc + N + n] : 0.f;
+    }
+    const float dtv = sel_softplus(dtr + (live ? hb_to_float(((const TW*)A.dt_bias)[c]) : 0.f));
+    const float dx = dtv * xv;
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < NPT; i++) {
+      const int n = ks + i * KS;
+      if (n < N) {
+        S[i] = fmaf(sel_decay(dtv, rate[i]), S[i], dx * Bn[i]);
+        acc = fmaf(S[i], Cn[i], acc);
+      }
+    }
+    for (int o = KS >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (live) {
+      if (ks == 0) ((TO*)A.out)[t * A.ldo + c] = hb_from_float<TO>(fmaf(dskip, xv, acc) * (zz / (1.f + expf(-zz))));
+#pragma unroll
+      for (int i = 0; i < NPT; i++) {
+        const int n = ks + i * KS;
+        if (n < N) st[n] = S[i];
+      }
+    }
+    return;
+  }
+  // how the block's threads tile a chunk's (token, channel) pairs: CPB is a power of two, so no division anywhere
+  const int cshift = __ffs(CPB) - 1, kk = threadIdx.x & (CPB - 1), jj = threadIdx.x >> cshift, jstep = SEL_THREADS >> cshift;
+  const int lane = threadIdx.x & 31, wrp = threadIdx.x >> 5;
   auto fetch = [&](int j0, float* b) {
     const int n = min(SEL_CH, len - j0);
-    for (int i = threadIdx.x; i < n * 2 * N; i += SEL_THREADS) {
-      const int j = i / (2 * N), k = i - j * 2 * N;
-      sel_cp4(b + j * row_w + k, A.bc + (size_t)(t0 + j0 + j) * A.ldbc + k);
+    const int nbc = MODE == SEL_PIECE_LOCAL ? N : 2 * N;          // a piece from a zero state needs no C
+    for (int j = wrp; j < n; j += SEL_THREADS / 32) {
+      const float* src = A.bc + (size_t)(t0 + j0 + j) * A.ldbc;
+      for (int k = lane; k < nbc; k += 32) sel_cp4(b + j * row_w + k, src + k);
     }
-    for (int i = threadIdx.x; i < n * nch; i += SEL_THREADS) {
-      const int j = i / nch, k = i - j * nch;
-      const size_t t = (size_t)(t0 + j0 + j);
-      float* row = b + j * row_w + 2 * N;
-      sel_cp4(row + k, A.dt + t * A.lddt + c0 + k);
-      sel_cp4(row + CPB + k, A.x + t * A.ldx + c0 + k);
-      sel_cp4(row + 2 * CPB + k, A.z + t * A.ldz + c0 + k);
+    if (kk < nch) {
+      for (int j = jj; j < n; j += jstep) {
+        const size_t t = (size_t)(t0 + j0 + j);
+        float* row = b + j * row_w + 2 * N;
+        sel_cp4(row + kk, A.dt + t * A.lddt + c0 + kk);
+        sel_cp4(row + CPB + kk, A.x + t * A.ldx + c0 + kk);
+        if (MODE != SEL_PIECE_LOCAL) sel_cp4(row + 2 * CPB + kk, A.z + t * A.ldz + c0 + kk);
+      }
     }
     sel_commit();
   };
   fetch(0, buf[0]);
-  const TW* dtb = (const TW*)A.dt_bias;
+  const float my_bias = kk < nch ? hb_to_float(((const TW*)A.dt_bias)[c0 + kk]) : 0.f;
   int which = 0;
   for (int j0 = 0; j0 < len; j0 += SEL_CH, which ^= 1) {
     float* b = buf[which];
@@ -129,10 +175,11 @@ __global__ void __launch_bounds__(SEL_THREADS) selective_scan_kernel(SelArgs A) 
     }
     __syncthreads();
     // the step sizes, once per (token, channel)
-    for (int i = threadIdx.x; i < n_tok * nch; i += SEL_THREADS) {
-      const int j = i / nch, k = i - j * nch;
-      float* p = b + j * row_w + 2 * N + k;
-      *p = sel_softplus(*p + hb_to_float(dtb[c0 + k]));
+    if (kk < nch) {
+      for (int j = jj; j < n_tok; j += jstep) {
+        float* p = b + j * row_w + 2 * N + kk;
+        *p = sel_softplus(*p + my_bias);
+      }
     }
     __syncthreads();
     for (int j = 0; j < n_tok; j++) {
@@ -145,24 +192,27 @@ __global__ void __launch_bounds__(SEL_THREADS) selective_scan_kernel(SelArgs A) 
       for (int i = 0; i < NPT; i++) {
         const int n = ks + i * KS;
         if (n < N) {
-          S[i] = fmaf(expf(dtv * rate[i]), S[i], dx * row[n]);
+          S[i] = fmaf(sel_decay(dtv, rate[i]), S[i], dx * row[n]);
           if (MODE != SEL_PIECE_LOCAL) acc = fmaf(S[i], row[N + n], acc);
         }
       }
       if (MODE != SEL_PIECE_LOCAL) {
         for (int o = KS >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-        if (ks == 0) {
-          const float zz = row[2 * N + 2 * CPB + cl];
-          b[j * row_w + 2 * N + 2 * CPB + cl] = fmaf(dskip, xv, acc) * (zz / (1.f + expf(-zz)));
-        }
+        // y takes the place of x (every lane of the channel has read x: the warp meets in between); the gate comes
+        // in the pass below, where every thread has an element of its own
+        __syncwarp();
+        if (ks == 0) b[j * row_w + 2 * N + CPB + cl] = fmaf(dskip, xv, acc);
       }
     }
     __syncthreads();
     if (MODE != SEL_PIECE_LOCAL) {
       TO* out = (TO*)A.out;
-      for (int i = threadIdx.x; i < n_tok * nch; i += SEL_THREADS) {
-        const int j = i / nch, k = i - j * nch;
-        out[(size_t)(t0 + j0 + j) * A.ldo + c0 + k] = hb_from_float<TO>(b[j * row_w + 2 * N + 2 * CPB + k]);
+      if (kk < nch) {
+        for (int j = jj; j < n_tok; j += jstep) {
+          const float* row = b + j * row_w + 2 * N;
+          const float zz = row[2 * CPB + kk];
+          out[(size_t)(t0 + j0 + j) * A.ldo + c0 + kk] = hb_from_float<TO>(row[CPB + kk] * (zz / (1.f + expf(-zz))));
+        }
       }
       __syncthreads();     // the buffer is asked for again two chunks on
     }
@@ -190,7 +240,7 @@ __global__ void __launch_bounds__(256) selective_carry_kernel(SelArgs A) {
   const int len = A.q_len[r];
   if (len <= 0) return;
   const int c = (int)(e / N), pieces = (len + A.L - 1) / A.L;
-  const float rate = -expf(hb_to_float(((const TW*)A.a_log)[e]));
+  const float rate = -expf(hb_to_float(((const TW*)A.a_log)[e])) * SEL_LOG2E;
   float* slot = A.state + (size_t)A.slot[r] * IN + e;
   float carry = *slot;
   const size_t base = (size_t)sel_piece_base(A.q_len, r, A.L);
@@ -202,7 +252,7 @@ __global__ void __launch_bounds__(256) selective_carry_kernel(SelArgs A) {
     for (int i = 0; i < 8; i++) {
       const bool in = k0 + i < pieces;
       own[i] = in ? ps[(size_t)(k0 + i) * IN] : 0.f;
-      dec[i] = in ? expf(rate * pd[(size_t)(k0 + i) * A.inner]) : 1.f;
+      dec[i] = in ? sel_decay(pd[(size_t)(k0 + i) * A.inner], rate) : 1.f;
     }
 #pragma unroll
     for (int i = 0; i < 8; i++) {
@@ -265,6 +315,31 @@ HB_EXPORT int hb_selective_scan(const float* x, long ldx, const float* dt, long 
   return 0;
 }
 
+// A 32-bit matrix as the sum of two bfloat16 matrices, hi = round(a) and lo = round(a - hi): two tensor-core products
+// with them, added in 32-bit, carry 16 bits of a's mantissa instead of 8 (the low-rank step sizes into their product).
+__global__ void __launch_bounds__(256) split_rounded_kernel(const float* __restrict__ a, long lda, __nv_bfloat16* __restrict__ hi,
+                                                            __nv_bfloat16* __restrict__ lo, long n, int K) {
+  hb_pdl_launch();
+  hb_pdl_wait();
+  for (long i = (long)blockIdx.x * 256 + threadIdx.x; i < n; i += (long)gridDim.x * 256) {
+    const long r = i / K;
+    const float v = a[r * lda + (i - r * K)];
+    const __nv_bfloat16 h = __float2bfloat16_rn(v);
+    hi[i] = h;
+    lo[i] = __float2bfloat16_rn(v - __bfloat162float(h));
+  }
+}
+
+// a float32 [M][K] with row stride lda; hi, lo bfloat16 [M][K] contiguous.
+HB_EXPORT int hb_split_rounded(const float* a, long lda, void* hi, void* lo, int M, int K, cudaStream_t s) {
+  if (M <= 0 || K <= 0) return 0;
+  const long n = (long)M * K;
+  const int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+  hb_launch(split_rounded_kernel, dim3(blocks), dim3(256), 0, s, a, lda, (__nv_bfloat16*)hi, (__nv_bfloat16*)lo, n, K);
+  HB_CHECK_LAUNCH("hb_split_rounded");
+  return 0;
+}
+
 // ---------------------------------------------------------------------------------------------------------------------
 // The residual row after a sublayer, in one pass:
 //     u = y                                                        a sublayer's plain result (or nothing)
@@ -281,8 +356,10 @@ __global__ void __launch_bounds__(256) residual_norm_kernel(float* __restrict__ 
                                                             const TW* __restrict__ wa, const TW* __restrict__ wb, float mix,
                                                             float pair_eps, float alpha, const float* __restrict__ w,
                                                             float eps, TO* __restrict__ xb, int W) {
-  extern __shared__ float rn_row[];      // [W], then 32 floats for the sums
+  extern __shared__ float rn_row[];      // [W], then 32 floats for the sums, then (a pair) [W] and [W]
   float* red = rn_row + W;
+  float* sa_row = red + 32;
+  float* sb_row = sa_row + W;
   hb_pdl_launch();
   hb_pdl_wait();
   const size_t base = (size_t)blockIdx.x * W;
@@ -291,6 +368,8 @@ __global__ void __launch_bounds__(256) residual_norm_kernel(float* __restrict__ 
     float sa = 0.f, sb = 0.f;
     for (int i = threadIdx.x; i < W; i += 256) {
       const float va = a[base + i], vb = b[base + i];
+      sa_row[i] = va;
+      sb_row[i] = vb;
       sa = fmaf(va, va, sa);
       sb = fmaf(vb, vb, sb);
     }
@@ -300,7 +379,7 @@ __global__ void __launch_bounds__(256) residual_norm_kernel(float* __restrict__ 
   float ss = 0.f;
   for (int i = threadIdx.x; i < W; i += 256) {
     float u = y ? y[base + i] : 0.f;
-    if (a) u += mix * (a[base + i] * fa * hb_to_float(wa[i]) + b[base + i] * fb * hb_to_float(wb[i]));
+    if (a) u += mix * (sa_row[i] * fa * hb_to_float(wa[i]) + sb_row[i] * fb * hb_to_float(wb[i]));
     const float v = fmaf(alpha, x[base + i], u);
     rn_row[i] = v;
     ss = fmaf(v, v, ss);
@@ -321,7 +400,7 @@ HB_EXPORT int hb_residual_norm(float* x, const float* y, const float* a, const f
                                int xb_dt, int T, int W, cudaStream_t s) {
   if (T <= 0) return 0;
   if ((a != nullptr) != (b != nullptr) || (a && (!wa || !wb))) HB_FAIL("hb_residual_norm: a pair needs both rows and both weights");
-  const size_t smem = (size_t)(W + 32) * sizeof(float);
+  const size_t smem = (size_t)((a ? 3 : 1) * W + 32) * sizeof(float);
   if (smem > 200 * 1024) HB_FAIL("hb_residual_norm: a row of %d does not fit shared memory", W);
   if (!a) pw_dt = HB_F32;
   if (!xb) xb_dt = HB_F32;

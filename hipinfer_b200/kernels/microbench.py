@@ -11,6 +11,9 @@ scripts/bench.py:126-212, and reports GB/s or TFLOP/s from algorithmic bytes and
     python -m hipinfer_b200.kernels.microbench attn_window --batch 8 --context 2048 --window 1024        (single rows)
     python -m hipinfer_b200.kernels.microbench attn_window --portion --tokens 2048 --window 1024         (a prompt portion)
     python -m hipinfer_b200.kernels.microbench layernorm|polynorm|scale_add --m 2048 --n 2048
+    python -m hipinfer_b200.kernels.microbench selective_scan --tokens 2048 --batch 1 --n 2048 --states 16   (a prompt portion)
+    python -m hipinfer_b200.kernels.microbench selective_scan --tokens 1 --batch 64 --n 2048 --states 16     (single rows)
+    python -m hipinfer_b200.kernels.microbench residual_norm --m 2048 --n 2048 [--pair]
 
 Between timed launches of kernels whose inputs fit in L2 a buffer larger than L2 is written
 (`--flush`, on by default) so that the figures are for operands coming from HBM.
@@ -61,7 +64,7 @@ def _prepared(fast, x, nw):
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
     ap.add_argument("kernel", choices=["gemm_tc", "gemm_stream", "rows_add", "rows_swiglu", "rows_qkv", "attn_decode", "flash_prefill", "flash_prefill_tc", "rmsnorm",
-                                       "delta_rule", "attn_window", "layernorm", "polynorm", "scale_add"])
+                                       "delta_rule", "attn_window", "layernorm", "polynorm", "scale_add", "selective_scan", "residual_norm"])
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=16384)
     ap.add_argument("--k", type=int, default=2048)
@@ -77,6 +80,8 @@ def main(argv=None) -> int:
     ap.add_argument("--window", type=int, default=1024, help="attn_window: the window (0: none); 4 first tokens are kept")
     ap.add_argument("--value-dim", type=int, default=64, help="attn_window: width of a head's values (a score map is --head-dim / 2 wide)")
     ap.add_argument("--portion", action="store_true", help="attn_window: one request's portion of --tokens rows instead of --batch single rows")
+    ap.add_argument("--states", type=int, default=16, help="selective_scan: states a channel (--n is the number of channels)")
+    ap.add_argument("--pair", action="store_true", help="residual_norm: two side-by-side results that are normed and joined")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-flush", dest="flush", action="store_false")
     ap.add_argument("--prepared-norm", action="store_true",
@@ -90,7 +95,34 @@ def main(argv=None) -> int:
     g = torch.Generator(device=dev).manual_seed(0)
     rnd = lambda *s: torch.randn(*s, generator=g, device=dev)
     out = {"kernel": a.kernel}
-    if a.kernel.startswith("rows"):
+    if a.kernel == "selective_scan":
+        from types import SimpleNamespace
+
+        R, L, I, N = a.batch, a.tokens, a.n, a.states
+        T = R * L
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+        x, dt, z, bc = rnd(T, I), rnd(T, I), rnd(T, I), rnd(T, 2 * N)
+        a_log = (torch.rand(I, N, generator=g, device=dev) * 5 - 4).bfloat16()
+        dt_bias, d = rnd(I).bfloat16(), rnd(I).bfloat16()
+        state, y = torch.zeros(R, I, N, device=dev), torch.empty(T, I, dtype=torch.bfloat16, device=dev)
+        batch = SimpleNamespace(n_requests=R, max_q_len=L, req_q_start=i32([r * L for r in range(R)]), req_q_len=i32([L] * R),
+                                req_state_slot=i32(list(range(R))))
+        fn = lambda: ops.selective_scan(x, dt, bc, z, dt_bias, a_log, d, state, batch, y)
+        ms = timeit(fn, a.iters, a.flush)
+        pieces = L >= 3 * ops.SEL_PIECE_TOKENS > 0
+        # rows in (x, dt, B | C, and z once) and out, the states in and out; in pieces x, dt and B are read twice
+        nbytes = T * (I * 4 * (5 if pieces else 3) + 2 * N * 4 * (1.5 if pieces else 1) + I * 2) + 2 * R * I * N * 4
+        out.update(requests=R, tokens=L, channels=I, states=N, pieces=bool(pieces), ms=ms, gbs=nbytes / ms / 1e6,
+                   us_per_token=ms * 1e3 / L)
+    elif a.kernel == "residual_norm":
+        M, W = a.m, a.n
+        x, y, w = rnd(M, W), rnd(M, W), 1 + 0.1 * rnd(W)
+        pair = ops.NormedPair(rnd(M, W), rnd(M, W), torch.ones(W, device=dev).bfloat16(), torch.ones(W, device=dev).bfloat16(), 0.5, 1e-5) if a.pair else None
+        rounded = torch.empty(M, W, dtype=torch.bfloat16, device=dev)
+        fn = lambda: ops.residual_norm(x, None if a.pair else y, pair, 2.0, w, 1e-5, rounded)
+        ms = timeit(fn, a.iters, a.flush)
+        out.update(m=M, n=W, pair=a.pair, ms=ms, gbs=M * W * (4 * (3 if a.pair else 2) + 4 + 2) / ms / 1e6)
+    elif a.kernel.startswith("rows"):
         M, N, K = a.m, a.n, a.k
         w = (rnd(N, K) * 0.02).bfloat16()
         nw = torch.ones(K, device=dev, dtype=torch.bfloat16)

@@ -69,6 +69,7 @@ _SIGS = {
         "hb_ssd_gate_norm": [_p, _p, _l, _p, _i, _p, _i, _i, _i, _i, _f, _p],
         "hb_selective_scan": [_p, _l, _p, _l, _p, _l, _p, _l, _p, _p, _p, _i, _p, _p, _p, _p, _p, _i, _l, _i, _i, _i, _i, _i, _p, _p,
                               _p],
+        "hb_split_rounded": [_p, _l, _p, _p, _i, _i, _p],
         "hb_residual_norm": [_p, _p, _p, _p, _p, _p, _i, _f, _f, _f, _p, _f, _p, _i, _i, _i, _p],
         "hb_moe_route": [_p, _i, _l, _p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _p],
         "hb_moe_gate_up_rows": [_p, _i, _l, _p, _i, _p, _p, _p, _i, _i, _i, _i, _i, _p],
@@ -1228,6 +1229,25 @@ def selective_scan(x: torch.Tensor, dt: torch.Tensor, bc: torch.Tensor, z: torch
           batch.req_q_start.data_ptr(), batch.req_q_len.data_ptr(), batch.req_state_slot.data_ptr(), out.data_ptr(), _dt(out),
           out.stride(0), batch.n_requests, inner, N, L, pieces, _ptr(piece_state), _ptr(piece_dt), _stream())
     return out
+
+
+def linear_split32(a: torch.Tensor, w: "Weight", out: torch.Tensor) -> torch.Tensor:
+    """out = a @ w.T for float32 rows a (a view of wider rows is fine) and float32 out. Where the weight is bfloat16 and
+    the tensor-core product takes the sizes, a goes in as the sum of two bfloat16 matrices (round(a) and round(a - round(a)))
+    through two products added in 32-bit: 16 bits of a's mantissa at tensor-core speed. Else the plain 32-bit product."""
+    from . import fast
+
+    _need_cuda(a, out)
+    _rows_contiguous(a, "linear_split32 a")
+    M, K = a.shape
+    if (a.dtype == torch.float32 and w.t.dtype == torch.bfloat16 and out.dtype == torch.float32 and M > 64 and K % 8 == 0
+            and not fast.PLAIN_ONLY):
+        hi = torch.empty(M, K, dtype=torch.bfloat16, device=a.device)
+        lo = torch.empty(M, K, dtype=torch.bfloat16, device=a.device)
+        _call("hybrid", "hb_split_rounded", a.data_ptr(), a.stride(0), hi.data_ptr(), lo.data_ptr(), M, K, _stream())
+        if fast.linear(hi, w, out, False) and fast.linear(lo, w, out, True):
+            return out
+    return linear(a, w, out)
 
 
 class NormedPair:

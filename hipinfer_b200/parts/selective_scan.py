@@ -72,7 +72,7 @@ class SelectiveScanMixer(Mixer):
         dbc = torch.empty(T, R + 2 * N, dtype=torch.float32, device=dev)
         ops.linear_rows32(xc if self.ctx.dtype == torch.float32 else ops.convert(xc, self.ctx.dtype), self.w_x, dbc)
         dt = torch.empty(T, I, dtype=torch.float32, device=dev)
-        ops.linear(dbc[:, :R], self.w_dt, dt)                 # the low-rank step sizes stay 32-bit into their product
+        ops.linear_split32(dbc[:, :R], self.w_dt, dt)         # the low-rank step sizes keep 16 bits or more into their product
         y = torch.empty(T, I, dtype=self.ctx.dtype, device=dev)
         ops.selective_scan(xc, dt, dbc[:, R:], proj[:, I:], self.dt_bias, self.a_log, self.d_skip, state["S"], batch, y)
         planes.record(batch, "attention", y)

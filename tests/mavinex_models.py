@@ -104,14 +104,16 @@ def draw_weights(config: dict, seed: int, dtype=torch.bfloat16, decisive_routers
     """{name: tensor} for `config` from the product's own list of tensors, rounded to `dtype` (so that the engine and the
     plain implementation start from the same numbers).
 
-    decisive_routers (default: when dtype is bfloat16): with random routers two logits nearly tie at a few positions of
-    every sequence, rounded inputs then choose another expert than exact ones, and a recurrent layer carries the
-    difference to every later position. So the first E channels of the width (E the largest number of experts) carry a
-    code that only the embedding writes: per token a permutation of E evenly spaced levels; no mixer or expert writes
+    decisive_routers (default: on): with random routers two logits nearly tie at a few positions of every sequence, inputs
+    that differ by rounding alone (bfloat16 against exact ones; in 32-bit a sum taken in another order) then choose
+    another expert, and a recurrent layer carries the difference to every later position. So the first E channels of the
+    width (E the largest number of experts) carry a code that only the embedding writes: per token a permutation of E
+    evenly spaced levels; no mixer or expert writes
     into these channels (those rows of their last matrices are zero, and the weights that follow the side-by-side norms
     are zero there), every norm multiplies them by one number (a row's scale keeps their order), and router row e reads
     channel e alone, without a bias. The experts' order then depends on the token only, with gaps of several percent
-    between neighbours, and the weights still differ from expert to expert and from token to token."""
+    between neighbours, and the weights still differ from expert to expert and from token to token. (Random routers with
+    their biases are compared in tests/test_gpu_mavinex_parts.py, row by row, with the nearly tied rows left out.)"""
     from hipinfer_b200.config import config_from_dict, get_architecture
     from hipinfer_b200.parts.spec import spec_param_specs
 
@@ -119,7 +121,7 @@ def draw_weights(config: dict, seed: int, dtype=torch.bfloat16, decisive_routers
     g = torch.Generator().manual_seed(seed)
     out = {}
     if decisive_routers is None:
-        decisive_routers = dtype == torch.bfloat16
+        decisive_routers = True
     code = max([L["mlp"]["router"]["experts"] for L in config["layers"] if L.get("mlp")], default=0)
     code = code if decisive_routers else 0
     for s in spec_param_specs(get_architecture(c.architecture).build_spec(c)):

@@ -281,6 +281,21 @@ def test_a_slow_decay_carries_a_far_token_and_a_fast_one_forgets_it():
     assert abs(float(out[T - 1, 1]) - 3.0 * dt * N * 30.0) < 1e-3 * 3.0 * dt * N * 30.0        # nothing of token 0 is left
 
 
+@pytest.mark.parametrize("M,K,N", [(200, 128, 96), (70, 16, 256), (300, 12, 64), (8, 128, 96)])
+def test_a_32_bit_product_through_two_rounded_halves(M, K, N):
+    """32-bit rows times a bfloat16 weight: as the sum of two bfloat16 matrices on the tensor cores where the sizes allow,
+    on the plain kernel otherwise; either way far closer than rounding the rows to bfloat16 would be."""
+    from hipinfer_b200.kernels import ops
+
+    wide = rnd(M, K + 5, seed=1)
+    a, w = wide[:, 5:], (rnd(N, K, seed=2) / math.sqrt(K)).bfloat16()
+    out = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    ops.linear_split32(wide.to(DEV)[:, 5:], ops.Weight(w.to(DEV)), out)
+    want = a.double() @ w.double().T
+    close(out, want, torch.float32, tol=3e-5)
+    assert float((a.bfloat16().double() @ w.double().T - want).abs().max()) > 1e-3 * float(want.abs().max())
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("W,I,N,R,K", [(64, 48, 8, 5, 4), (50, 18, 7, 2, 5), (128, 256, 16, 8, 3), (48, 24, 12, 3, 1), (96, 80, 3, 1, 7)])
 def test_selective_mixer_part(dtype, W, I, N, R, K):
