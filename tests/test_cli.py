@@ -102,3 +102,33 @@ def test_generate_serves_the_second_architecture(tmp_path):
     shape = ast.literal_eval(lines[-2])
     assert shape["vocab"] == cfg["vocab"] and shape["hidden"] == cfg["width"] and shape["layers"] == len(cfg["layers"])
     assert ast.literal_eval(lines[-1]) == want
+
+
+@pytest.mark.gpu
+def test_generate_serves_the_mavinex_architecture(tmp_path):
+    """The same command on a Mavinex folder (a layer run three times with one layer's tensors, side-by-side mixers, latent
+    attention with a sink, experts): prompt portions of 8 tokens through the scheduler, then greedy decoding, in 32-bit
+    against the plain implementation; a different token is accepted only where the plain logits nearly tie."""
+    import mavinex_models as tm
+
+    folder, cfg, w = tm.make_folder(tmp_path / "model", "a", seed=5, dtype=torch.float32)
+    prompt = tiny.random_tokens(29, cfg["vocab"], 8)
+    model = tm.PlainMavinex(cfg, w)
+    logits, want, steps = model.forward(prompt)[-1], [], []
+    for _ in range(6):
+        steps.append(logits)
+        want.append(int(logits.argmax()))
+        logits = model.forward([want[-1]])[-1]
+    r = run([sys.executable, "-m", "hipinfer_b200", "generate", "--model", folder, "--tokens", *map(str, prompt), "--new", "6",
+             "--mode", "fp32", "--max-seq", "64", "--max-batch", "2", "--max-prefill", "8"])
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = r.stdout.strip().splitlines()
+    shape = ast.literal_eval(lines[-2])
+    assert shape["vocab"] == cfg["vocab"] and shape["hidden"] == cfg["width"]
+    got = ast.literal_eval(lines[-1])
+    for i, (g, t) in enumerate(zip(got, want)):
+        if g != t:
+            top = torch.topk(steps[i].float(), 2).values
+            assert float(top[0] - top[1]) < 1e-3 * float(steps[i].abs().max()), (i, got, want)
+            break
+    assert len(got) == len(want)
