@@ -143,6 +143,75 @@ def test_whole_row_norm_then_interleaved_rotation_and_cache_write(dtype, H, G, D
         close(vc[page, :, off], p64[t, o[2]:].reshape(G, E), dtype, f"v of row {t}")
 
 
+def _paged_kv(keys, values, ps, dtype, seed):
+    """Planes [page, kv head, ps, width] of requests' keys [n, G, D] and values [n, G, E] on shuffled pages, and block tables."""
+    n_pages = [-(-k.shape[0] // ps) for k in keys]
+    order = torch.randperm(sum(n_pages) + 2, generator=torch.Generator().manual_seed(seed)).tolist()
+    G, D, E = keys[0].shape[1], keys[0].shape[2], values[0].shape[2]
+    kc, vc = torch.zeros(len(order), G, ps, D, dtype=dtype), torch.zeros(len(order), G, ps, E, dtype=dtype)
+    bt = torch.full((len(keys), max(n_pages)), -1, dtype=torch.int32)
+    it = iter(order)
+    for r in range(len(keys)):
+        for lp in range(n_pages[r]):
+            page = next(it)
+            bt[r, lp] = page
+            m = min(ps, keys[r].shape[0] - lp * ps)
+            kc[page, :, :m] = keys[r][lp * ps:lp * ps + m].transpose(0, 1).to(dtype)
+            vc[page, :, :m] = values[r][lp * ps:lp * ps + m].transpose(0, 1).to(dtype)
+    return kc.to(DEV), vc.to(DEV), bt.to(DEV)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,G,D,E,window", [(6, 3, 64, 80, 136), (4, 1, 32, 32, 24), (2, 2, 16, 24, 1), (8, 2, 64, 64, 200), (3, 1, 10, 6, 37)])
+def test_grouped_heads_see_exactly_the_window_in_decoding_and_in_a_portion(dtype, H, G, D, E, window):
+    """Keys of kv head 0 just inside the window get a large score with head 0's query and the key just outside a larger
+    one; values wider or narrower than keys; a gate per element. Single rows over the pages (positions at the window's
+    edge, at a page's edge, the first tokens, far behind the window) and the same rows as ONE portion behind a cached
+    context: one position off in either direction and the result is another vector."""
+    from hipinfer_b200.kernels import ops
+
+    ps, n = 16, window + 170
+    ctx = window + 23                                           # the portion is rows [ctx, n)
+    keys, vals = rnd(n, G, D, seed=1) * 0.5, rnd(n, G, E, seed=2)
+    q = rnd(n, H, D, seed=3) * 0.5
+    marked = sorted({0, 1, window - 1, window, window + 1, ctx - 1, ctx, ctx + 1, ctx + 15, ctx + 16, n - 1} & set(range(n)))
+    for p in marked[::2]:                                       # every second one, so that marks do not sit in each other's windows
+        u = q[p, 0] / q[p, 0].norm()
+        if p - window + 1 >= 0:
+            keys[p - window + 1, 0] = 6.0 * u
+        if p - window >= 0:
+            keys[p - window, 0] = 9.0 * u
+    gate = rnd(n, 3 + H * E, seed=4) * 2
+    kc, vc, bt = _paged_kv([keys], [vals], ps, dtype, 5)
+    scale = 1.0 / math.sqrt(D)
+    kd, vd, qd = keys.to(dtype).double(), vals.to(dtype).double(), q.to(dtype).double()
+    seen = plain.visible(n, window)
+
+    def want_rows(rows):
+        out = []
+        for p in rows:
+            heads = [plain.softmax_with_sink((kd[:, h // (H // G)] @ qd[p, h])[None] * scale, seen[p][None])[0] @ vd[:, h // (H // G)]
+                     for h in range(H)]
+            out.append(torch.cat(heads) * torch.sigmoid(gate[p, 3:].double()))
+        return torch.stack(out)
+
+    # decoding: every marked row alone
+    batch = SimpleNamespace(block_tables=[bt], row_request=i32([0] * len(marked)), positions=i32(marked), req_q_len=i32([1]),
+                            h_q_len=[1], max_q_len=1, max_pos=n - 1, n_requests=1, extra={})
+    out = torch.empty(len(marked), H * E, dtype=dtype, device=DEV)
+    ops.attention_masked(q[marked].reshape(len(marked), H * D).to(dtype).to(DEV), kc, vc, batch, 0, out, H, G, D, E, ps, scale, "window",
+                         window=window, gate=gate[marked].to(DEV), gate_offset=3)
+    close(out, want_rows(marked), dtype, "single rows")
+    # a portion: rows ctx .. n - 1 in one step behind ctx cached tokens
+    rows = list(range(ctx, n))
+    batch = batch_of([len(rows)], ctx=[ctx])
+    batch.block_tables, batch.extra = [bt], {}
+    out = torch.empty(len(rows), H * E, dtype=dtype, device=DEV)
+    ops.attention_masked(q[ctx:].reshape(len(rows), H * D).to(dtype).to(DEV), kc, vc, batch, 0, out, H, G, D, E, ps, scale, "window",
+                         window=window, gate=gate[ctx:].to(DEV), gate_offset=3)
+    close(out, want_rows(rows), dtype, "portion")
+
+
 # ------------------------------------------------------------------------------------------ the selective recurrence
 def _scan_inputs(T, I, N, seed):
     x, dt_raw, bc, z = rnd(T, I, seed=seed), rnd(T, I, seed=seed + 1), rnd(T, 2 * N, seed=seed + 2), rnd(T, I, seed=seed + 3)
