@@ -288,7 +288,7 @@ def _random_config(seed):
             dim = pick([16, 32, 64, 80, 128])
             layers.append(tm.parallel(
                 tm.attention(kv * pick([1, 2, 3]), kv, dim, pick([16, 32, 64, 80, 128]), window=window, rot_dims=pick([dim, dim // 2, 0]),
-                             base=pick([100.0, 10000.0, 250000.0]), scaling=pick([None, tm.bands(pick([2.0, 8.0, 32.0]), pick([16, 64, 256]))])),
+                             base=pick([100.0, 10000.0, 500000.0]), scaling=pick([None, tm.bands(pick([2.0, 8.0, 32.0]), pick([16, 64, 256]))])),
                 tm.scan(pick([32, 64, 96, 160, 256]), pick([4, 8, 16, 24, 64]), pick([1, 4, 8, 12, 16]), conv=pick([2, 3, 4])), mlp=mlp))
     for i in range(len(layers)):
         if rng.random() < 0.4:

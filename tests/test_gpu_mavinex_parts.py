@@ -85,9 +85,9 @@ def test_norm_part_with_a_weight_stored_around_zero():
 
 
 # ------------------------------------------------------------------------------------------ rotation tables
-@pytest.mark.parametrize("dims,base,sc", [(64, 250000.0, dict(kind="wavelength_bands", factor=8.0, low=1.0, high=4.0, original=1024)),
+@pytest.mark.parametrize("dims,base,sc", [(64, 200000.0, dict(kind="wavelength_bands", factor=6.0, low=1.0, high=4.0, original=2048)),
                                           (16, 10000.0, dict(kind="wavelength_bands", factor=4.0, low=2.0, high=8.0, original=40)),
-                                          (32, 10000.0, dict(kind="yarn", factor=2.0, original=512, fast=32.0, slow=1.0)),
+                                          (32, 10000.0, dict(kind="yarn", factor=3.0, original=256, fast=32.0, slow=1.0)),
                                           (8, 100.0, dict(kind="yarn", factor=40.0, original=16, fast=4.0, slow=2.0)),
                                           (12, 5000.0, None)])
 def test_rotation_tables_with_rescaled_frequencies(dims, base, sc):
@@ -110,7 +110,7 @@ def test_rotation_tables_with_rescaled_frequencies(dims, base, sc):
 
 # ------------------------------------------------------------------------------------------ attention: row norm, rotation
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,G,D,E,rot", [(6, 2, 64, 80, 64), (3, 1, 10, 6, 6), (4, 4, 32, 32, 16), (2, 1, 128, 24, 0)])
+@pytest.mark.parametrize("H,G,D,E,rot", [(6, 2, 64, 96, 64), (3, 1, 10, 6, 6), (4, 4, 32, 32, 16), (2, 1, 128, 24, 0)])
 def test_whole_row_norm_then_interleaved_rotation_and_cache_write(dtype, H, G, D, E, rot):
     """q and k are divided by the root mean square of their WHOLE rows (all heads at once) and multiplied by a weight per
     column before the rotation of pairs (2i, 2i + 1); a norm per head instead would give other numbers (checked)."""
@@ -162,7 +162,7 @@ def _paged_kv(keys, values, ps, dtype, seed):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,G,D,E,window", [(6, 3, 64, 80, 136), (4, 1, 32, 32, 24), (2, 2, 16, 24, 1), (8, 2, 64, 64, 200), (3, 1, 10, 6, 37)])
+@pytest.mark.parametrize("H,G,D,E,window", [(6, 2, 64, 96, 120), (4, 1, 32, 32, 24), (2, 2, 16, 24, 1), (8, 2, 64, 64, 200), (3, 1, 10, 6, 37)])
 def test_grouped_heads_see_exactly_the_window_in_decoding_and_in_a_portion(dtype, H, G, D, E, window):
     """Keys of kv head 0 just inside the window get a large score with head 0's query and the key just outside a larger
     one; values wider or narrower than keys; a gate per element. Single rows over the pages (positions at the window's
@@ -226,7 +226,7 @@ def _scan_plain(x, dt_raw, bc, z, a_log, dt_bias, d, N):
     return y * plain.silu(z.double())
 
 
-@pytest.mark.parametrize("I,N", [(48, 8), (18, 7), (30, 5), (24, 1), (96, 16), (384, 24), (64, 40), (256, 128), (40, 200), (80, 3)])
+@pytest.mark.parametrize("I,N", [(48, 8), (18, 7), (30, 5), (24, 1), (96, 16), (320, 24), (64, 40), (256, 128), (40, 200), (80, 3)])
 def test_selective_recurrence_against_the_plain_scan(I, N):
     """Three requests of unequal lengths in one step, then single tokens that go on from the states the step left; a slot
     that another request used before starts clean only because the caller zeroes it (checked: the state is carried)."""
