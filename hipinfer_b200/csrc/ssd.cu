@@ -15,14 +15,14 @@
 // from a CUDA graph; where a portion or a piece starts changes a token's result by rounding only.
 #include "common.cuh"
 
-constexpr int SC_TAPS_MAX = 8;     // most convolution taps
+constexpr int SC_TAPS_MAX = 16;    // most convolution taps (the kernel is built for up to 8 and for up to 16)
 constexpr int SC_CHUNK = 64;       // tokens a block of the convolution walks
 constexpr int SC_THREADS = 128;
 
 // grid (channel tiles, requests, token chunks); a thread owns a channel and walks its chunk's tokens with the K - 1 raw
 // inputs before them in registers. Only the block of a request's first chunk reads the carried inputs, and it alone writes
 // the new ones, after it has read the old: nothing else in the launch touches them.
-template <typename TW>
+template <typename TW, int TAPS>
 __global__ void __launch_bounds__(SC_THREADS) ssd_conv_kernel(const float* __restrict__ proj, long ld, int off,
                                                               const TW* __restrict__ w, const TW* __restrict__ bias,
                                                               float* __restrict__ carried, const int* __restrict__ q_start,
@@ -35,26 +35,26 @@ __global__ void __launch_bounds__(SC_THREADS) ssd_conv_kernel(const float* __res
   if (c >= C || j0 >= len) return;
   const int t0 = q_start[r], K1 = K - 1;
   float* st = carried + (size_t)slot[r] * K1 * C + c;          // [K - 1][C], oldest first
-  float wk[SC_TAPS_MAX], hist[SC_TAPS_MAX], old[SC_TAPS_MAX];
+  float wk[TAPS], hist[TAPS], old[TAPS];
 #pragma unroll
-  for (int k = 0; k < SC_TAPS_MAX; k++) wk[k] = k < K ? hb_to_float(w[(size_t)c * K + k]) : 0.f;
+  for (int k = 0; k < TAPS; k++) wk[k] = k < K ? hb_to_float(w[(size_t)c * K + k]) : 0.f;
   const float bs = hb_to_float(bias[c]);
   const float* in = proj + (size_t)t0 * ld + off + c;
   // hist[i]: the raw input i + 1 tokens before the current one
 #pragma unroll
-  for (int i = 0; i < SC_TAPS_MAX - 1; i++) {
+  for (int i = 0; i < TAPS - 1; i++) {
     old[i] = (blockIdx.z == 0 && i < K1) ? st[(size_t)i * C] : 0.f;
     hist[i] = 0.f;
   }
 #pragma unroll
-  for (int i = 0; i < SC_TAPS_MAX - 1; i++) {
+  for (int i = 0; i < TAPS - 1; i++) {
     if (i < K1) {
       const int j = j0 - 1 - i;
       if (j >= 0) hist[i] = in[(size_t)j * ld];
       else {
         float v = 0.f;                                         // old[K1 + j], a dynamic index kept out of local memory
 #pragma unroll
-        for (int q = 0; q < SC_TAPS_MAX - 1; q++) v = (q == K1 + j) ? old[q] : v;
+        for (int q = 0; q < TAPS - 1; q++) v = (q == K1 + j) ? old[q] : v;
         hist[i] = v;
       }
     }
@@ -64,12 +64,12 @@ __global__ void __launch_bounds__(SC_THREADS) ssd_conv_kernel(const float* __res
     const float cur = in[(size_t)(j0 + j) * ld];
     float acc = bs;
 #pragma unroll
-    for (int i = SC_TAPS_MAX - 2; i >= 0; i--)
+    for (int i = TAPS - 2; i >= 0; i--)
       if (i < K1) acc = fmaf(wk[K1 - 1 - i], hist[i], acc);    // tap k multiplies the input K - 1 - k tokens back
     acc = fmaf(wk[K1], cur, acc);
     out[(size_t)(t0 + j0 + j) * C + c] = acc / (1.f + expf(-acc));
 #pragma unroll
-    for (int i = SC_TAPS_MAX - 2; i > 0; i--) hist[i] = hist[i - 1];
+    for (int i = TAPS - 2; i > 0; i--) hist[i] = hist[i - 1];
     hist[0] = cur;
   }
   if (blockIdx.z == 0) {
@@ -80,7 +80,7 @@ __global__ void __launch_bounds__(SC_THREADS) ssd_conv_kernel(const float* __res
       else {
         v = 0.f;
 #pragma unroll
-        for (int q = 0; q < SC_TAPS_MAX - 1; q++) v = (q == K1 + j) ? old[q] : v;
+        for (int q = 0; q < TAPS - 1; q++) v = (q == K1 + j) ? old[q] : v;
       }
       st[(size_t)k * C] = v;
     }
@@ -94,9 +94,15 @@ HB_EXPORT int hb_ssd_conv(const float* proj, long ld, int off, const void* w, co
   if (K < 1 || K > SC_TAPS_MAX) HB_FAIL("hb_ssd_conv: %d taps (1 to %d are supported)", K, SC_TAPS_MAX);
   dim3 grid((C + SC_THREADS - 1) / SC_THREADS, n_requests, (max_q_len + SC_CHUNK - 1) / SC_CHUNK);
   if (grid.y > 65535 || grid.z > 65535) HB_FAIL("hb_ssd_conv: the grid is too large");
-  HB_DISPATCH_1(w_dt, "hb_ssd_conv",
-                (hb_launch(ssd_conv_kernel<TA>, grid, dim3(SC_THREADS), 0, s, proj, ld, off, (const TA*)w, (const TA*)bias, carried,
-                           q_start, q_len, slot, out, C, K)));
+  if (K <= 8) {
+    HB_DISPATCH_1(w_dt, "hb_ssd_conv",
+                  (hb_launch(ssd_conv_kernel<TA, 8>, grid, dim3(SC_THREADS), 0, s, proj, ld, off, (const TA*)w, (const TA*)bias, carried,
+                             q_start, q_len, slot, out, C, K)));
+  } else {
+    HB_DISPATCH_1(w_dt, "hb_ssd_conv",
+                  (hb_launch(ssd_conv_kernel<TA, 16>, grid, dim3(SC_THREADS), 0, s, proj, ld, off, (const TA*)w, (const TA*)bias, carried,
+                             q_start, q_len, slot, out, C, K)));
+  }
   HB_CHECK_LAUNCH("hb_ssd_conv");
   return 0;
 }

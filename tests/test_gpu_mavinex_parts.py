@@ -366,7 +366,7 @@ def test_a_32_bit_product_through_two_rounded_halves(M, K, N):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("W,I,N,R,K", [(64, 48, 8, 5, 4), (50, 18, 7, 2, 5), (128, 256, 16, 8, 3), (48, 24, 12, 3, 1), (96, 80, 3, 1, 7)])
+@pytest.mark.parametrize("W,I,N,R,K", [(64, 48, 8, 5, 4), (50, 18, 7, 2, 5), (128, 256, 16, 8, 3), (48, 24, 12, 3, 1), (96, 80, 3, 1, 7), (64, 40, 6, 4, 11)])
 def test_selective_mixer_part(dtype, W, I, N, R, K):
     """The whole mixer through its part: a portion of two requests, then single tokens from the states and the carried
     convolution inputs it left."""
@@ -379,7 +379,7 @@ def test_selective_mixer_part(dtype, W, I, N, R, K):
     for s in part.param_specs():
         leaf = s.name[len("p.mix."):]
         t = torch.randn(s.shape, generator=g)
-        w[leaf] = ({"A_log": torch.rand(s.shape, generator=g) * 5 - 4, "D": 1 + 0.5 * t, "conv": 0.6 * t, "conv.b": 0.5 * t, "dt.b": 0.5 * t}
+        w[leaf] = ({"A_log": torch.rand(s.shape, generator=g) * 5 - 4, "D": 1 + 0.5 * t, "conv": (1.2 / math.sqrt(K)) * t, "conv.b": 0.5 * t, "dt.b": 0.5 * t}
                    .get(leaf, t * (1.2 / math.sqrt(s.shape[-1])))).to(dtype)
     part.load({"p.mix." + k: v.to(DEV) for k, v in w.items()})
     lens, tail = [37, 6], 3

@@ -99,7 +99,7 @@ def test_gate_with_biases_and_limits(dtype, I, group):
 
 # ------------------------------------------------------------------------------------------ the state-space mixer
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("C,K", [(40, 4), (130, 1), (7, 2), (300, 7)])
+@pytest.mark.parametrize("C,K", [(40, 4), (130, 1), (7, 2), (300, 7), (33, 8), (50, 9), (20, 16)])
 def test_causal_convolution_carries_its_last_inputs(dtype, C, K):
     """Two requests, cut into portions of 1 to 70 rows (also shorter than the filter): every portion continues from the
     carried inputs of the one before; slots are used in another order than the requests."""
